@@ -1,0 +1,295 @@
+#!/usr/bin/env python
+"""Benchmark of the fused decode sampler: bf16 logits [256, 128256] per GPU -> token ids.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one fused-sampler call over one batch (256 rows per GPU, weak scaling:
+batch rows are independent, each rank samples its own batch, no collective on the data
+path).  Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
+the reference's algorithm on the host cores instead (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+B, V = 256, 128256          # benchmark configuration: decode batch and vocabulary (Llama-3 sized)
+N_SETS = 4                  # rotating input sets: 4 x 65.7 MB of logits > 126 MB L2, so every step reads HBM
+ALGO_BYTES = B * V * 2 + B * 12 + B * 4   # logits once + three parameter vectors + tokens out
+METRIC, UNIT = "sampled_tokens_per_s", "tokens/s"
+WORKLOAD = ("fused temperature/top-k/top-p/noise sampling, bf16 logits [256,128256] = N(0,sigma=3) + 10 at 8 "
+            "columns per row, T~U[0.5,1.5], top_k~U{1..1024} with 10% disabled, top_p~U[0.6,1), explicit f32 "
+            "uniform noise [256,128256]")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_inputs(torch, device, seed):
+    """One synthetic input set with the configuration's shapes and distributions, made on the device."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    x = torch.randn((B, V), generator=g, device=device, dtype=torch.float32) * 3.0
+    cols = torch.rand((B, V), generator=g, device=device).argsort(dim=1)[:, :8]
+    x.scatter_add_(1, cols, torch.full((B, 8), 10.0, device=device))
+    logits = x.to(torch.bfloat16)
+    temperature = torch.rand(B, generator=g, device=device) + 0.5
+    top_k = torch.randint(1, 1025, (B,), generator=g, device=device, dtype=torch.int32)
+    top_k[torch.rand(B, generator=g, device=device) < 0.1] = 0
+    top_p = torch.rand(B, generator=g, device=device) * 0.4 + 0.6
+    noise = torch.rand((B, V), generator=g, device=device, dtype=torch.float32)
+    return logits, top_k, top_p, temperature, noise
+
+
+def to_numpy(t):
+    import torch
+    if t.dtype == torch.bfloat16:
+        import ml_dtypes
+        return t.cpu().view(torch.int16).numpy().view(ml_dtypes.bfloat16)
+    return t.cpu().numpy()
+
+
+_REF_DATA = None
+
+
+def _oracle_rows(i):
+    from oracle import tallax_oracle as o
+    x, tk, tp, T, noise, stride = _REF_DATA
+    return o.sample(x[i::stride], tk[i::stride], tp[i::stride], T[i::stride], noise=noise[i::stride])
+
+
+def run_reference(args):
+    """CPU arm: the NumPy restatement of the reference's algorithm, rows spread over all host cores."""
+    global _REF_DATA
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import multiprocessing as mp
+    from oracle import tallax_oracle as o
+    cores = os.cpu_count() or 1
+    rows = 64  # bounded sample of the 256-row batch per step
+    workers = min(cores, rows)
+    _REF_DATA = (*o.make_sampling_inputs(B=rows, V=V, seed=2, dtype="bf16"), workers)
+    chunks = list(range(workers))
+    with mp.get_context("fork").Pool(workers) as pool:  # forked after the data exists: workers inherit it
+        for _ in range(args.warmup):
+            pool.map(_oracle_rows, chunks)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            pool.map(_oracle_rows, chunks)
+        dt = time.perf_counter() - t0
+    value = rows * args.steps / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "batch_per_step": rows},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": len(chunks), "kind": "port",
+                         "sample": f"{rows} of the 256 rows per step, NumPy restatement (JAX is not installable here)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sampler has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    from tallax_b200 import _lib, sampling
+    from tallax_b200._src import ops
+    _lib.load()
+
+    sets = [make_inputs(torch, device, seed=1000 * rank + s) for s in range(N_SETS)]
+    ws = ops.SampleWorkspace(B, V, device)
+    meta = [sampling.SamplingMetadata(top_k=s[1], top_p=s[2], temperature=s[3]) for s in sets]
+
+    def step(i):
+        s = sets[i % N_SETS]
+        return sampling.sample(None, s[0], meta[i % N_SETS], noise=s[4], workspace=ws)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        time.sleep(0.15)
+        barrier()
+        start.record()
+        for i in range(args.steps):
+            step(i)
+        stop.record()
+        barrier()
+        time.sleep(0.1)
+    ms = start.elapsed_time(stop)
+
+    # ---- end to end through the public API from pinned host buffers --------------------------
+    h_logits = torch.empty((B, V), dtype=torch.bfloat16).pin_memory()
+    h_noise = torch.empty((B, V), dtype=torch.float32).pin_memory()
+    h_params = [torch.empty(B, dtype=t.dtype).pin_memory() for t in sets[0][1:4]]
+    h_logits.copy_(sets[0][0]); h_noise.copy_(sets[0][4])
+    for h, t in zip(h_params, sets[0][1:4]):
+        h.copy_(t)
+    d_logits, d_noise = torch.empty_like(sets[0][0]), torch.empty_like(sets[0][4])
+    d_params = [torch.empty_like(t) for t in sets[0][1:4]]
+    h_tokens = torch.empty(B, dtype=torch.int32).pin_memory()
+
+    def e2e_step():
+        d_logits.copy_(h_logits, non_blocking=True)
+        d_noise.copy_(h_noise, non_blocking=True)
+        for d, h in zip(d_params, h_params):
+            d.copy_(h, non_blocking=True)
+        md = sampling.SamplingMetadata(top_k=d_params[0], top_p=d_params[1], temperature=d_params[2])
+        tok = sampling.sample(None, d_logits, md, noise=d_noise, workspace=ws)
+        h_tokens.copy_(tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller needs the token ids before the next decode step
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = times.tolist()
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        per_step_s = ms / 1e3 / args.steps
+        achieved = ALGO_BYTES / per_step_s / 1e9
+        # CPU baseline on a bounded sample of the same workload (rank 0, one core), also a parity spot check
+        from oracle import tallax_oracle as o
+        n_cpu = 48
+        s0 = sets[0]
+        xs, tk, tp, T = (to_numpy(t[:n_cpu]) for t in s0[:4])
+        nz = to_numpy(s0[4][:n_cpu])
+        t0 = time.perf_counter()
+        exp, flags = o.sample(xs, tk, tp, T, noise=nz, return_flags=True)
+        cpu_dt = time.perf_counter() - t0
+        got = to_numpy(sampling.sample(None, s0[0], meta[0], noise=s0[4])[:n_cpu])
+        mismatches = int(((got != exp) & ~flags).sum())
+        line = {
+            "metric": METRIC, "value": world * B * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch_per_gpu": B, "vocab": V, "sharding": f"batch rows x{world}",
+                       "l2": f"{N_SETS} rotating input sets ({N_SETS * B * V * 2 / 1e6:.0f} MB of logits > 126 MB L2)"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
+                    "h2d_bytes_per_step": B * V * 2 + B * V * 4 + B * 12, "d2h_bytes_per_step": B * 4,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src,
+                         "note": "algorithmic bytes of one sampler call / mean duration of the call's two kernels "
+                                 "(fast kernel + general kernel), CUDA events on the launching stream"},
+            "cpu_baseline": {"value": n_cpu / cpu_dt, "unit": UNIT, "cores": 1, "kind": "port",
+                             "sample": f"first {n_cpu} rows of input set 0, NumPy restatement of the reference "
+                                       f"(JAX not installable here); {mismatches} token mismatches vs the GPU "
+                                       f"outside the 1e-6 top-p exemption"},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,185 @@
+/* tallax_b200 -- C ABI of the B200 (sm_100a) row-wise select / sort / sample library.
+ *
+ * Every entry point
+ *   - takes raw device pointers, sizes and a CUDA stream (passed as void* so that
+ *     this header needs no CUDA include);
+ *   - only enqueues work on that stream: no allocation, no synchronisation, no host
+ *     read of device data (scratch memory is an explicit `workspace` argument whose
+ *     size the matching `*_workspace_bytes` function reports);
+ *   - returns TLX_OK or a negative error code; `tlx_last_error()` gives the message
+ *     of the calling thread's last failure.  Device code never traps: waits are
+ *     bounded and failures are reported through status words.
+ *
+ * The reference project (oliverdutton/tallax) has no C or FFI boundary: its device
+ * boundary is the `pl.pallas_call` site of each operator.  Each declaration below
+ * names the call site (path inside the reference project) that it replaces.
+ */
+#ifndef TALLAX_B200_H_
+#define TALLAX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TLX_ABI_VERSION 1
+
+typedef enum {
+  TLX_OK = 0,
+  TLX_ERR_INVALID = -1,     /* bad argument (maps to ValueError)            */
+  TLX_ERR_UNSUPPORTED = -2, /* valid but not built (NotImplementedError)    */
+  TLX_ERR_WORKSPACE = -3,   /* workspace missing or too small               */
+  TLX_ERR_CUDA = -4         /* a CUDA runtime call failed                   */
+} tlx_status;
+
+typedef enum {
+  TLX_F32 = 0,
+  TLX_BF16 = 1,
+  TLX_I32 = 2,
+  TLX_F16 = 3,
+  TLX_U32 = 4
+} tlx_dtype;
+
+int tlx_abi_version(void);
+const char* tlx_last_error(void);
+
+/* ---- gather --------------------------------------------------------------------
+ * out[b,j] = values[b, idx[b,j]] (axis 1) or out[i,b] = values[idx[i,b], b] (axis 0);
+ * an index outside [0, extent) yields 0, as the reference does.
+ * Replaces tallax/_src/gather.py:76-83 (pallas_call of take_along_axis_refs).       */
+int tlx_take_along_axis(void* stream, const void* values, const int32_t* indices, void* out,
+                        int64_t val_rows, int64_t val_cols, int64_t idx_rows, int64_t idx_cols,
+                        int elem_bytes, int axis);
+
+/* ---- cumsum --------------------------------------------------------------------
+ * Inclusive prefix sum along `axis` (0 or 1), optionally reversed.  dtype: F32, I32.
+ * Replaces tallax/_src/cumsum.py:93-101.                                             */
+int tlx_cumsum(void* stream, const void* in, void* out, int64_t rows, int64_t cols, int dtype,
+               int axis, int reverse);
+
+/* ---- arg-max with lowest-index tie break ---------------------------------------
+ * out_idx[r] = arg-max over columns (axis 1) or out_idx[c] = arg-max over rows
+ * (axis 0) in the order-preserving key domain.  The payload-carrying form of the
+ * reference (tallax/_src/bitonic_top_k.py:43-97 max_arrays) is this index plus a
+ * gather of every operand.                                                          */
+int tlx_argmax(void* stream, const void* keys, int dtype, int64_t rows, int64_t cols, int axis,
+               int32_t* out_idx);
+
+/* ---- sort ----------------------------------------------------------------------
+ * Stable row-wise argsort of one key array [rows, n] (dtype F32, BF16, F16, I32, U32),
+ * ascending or descending; ties always keep ascending position.  If `in_perm` is
+ * given, row r sorts key[r, in_perm[r, :]] and the result permutation is composed
+ * with it (least-significant-key-first chaining gives multi-key sorts).
+ * out_keys (nullable): the sorted keys, canonicalised (-0 -> +0, one NaN).
+ * out_perm (nullable): int32 source column of every output position.
+ * Replaces tallax/_src/sort.py:559-571 and :740-758 (the VMEM sort and the HBM
+ * substage kernels behind `sort`, sort.py:768-929).                                 */
+size_t tlx_sort_workspace_bytes(int64_t rows, int64_t n);
+int tlx_sort(void* stream, const void* keys, int dtype, int64_t rows, int64_t n, int descending,
+             const int32_t* in_perm, void* out_keys, int32_t* out_perm, void* workspace,
+             size_t workspace_bytes);
+
+/* ---- top-k ---------------------------------------------------------------------
+ * Row-wise descending top-`k_max` of x[rows, n] (row stride in elements), ties broken
+ * by lower index; out_vals keeps the input dtype, out_idx is int32, both [rows, k_max].
+ * k_per_row (nullable, device int32[rows]) with use_replace != 0: positions >= k[row]
+ * receive replace_val in out_vals.
+ * mode 0 = exact.  mode 1 = single-pass only (the reference's guarantee_convergence=False
+ * contract): rows whose candidate buffer overflowed are answered from the candidates
+ * seen, out_valid[0] is cleared, out_depths[row] is the number of threshold
+ * refinements and out_cutoff[row] (f32 for float input, i32 for int) the final
+ * candidate threshold.  out_valid/out_depths/out_cutoff may be NULL in mode 0.
+ * Replaces tallax/_src/top_k.py:482-506 (top_dynamic_k) and
+ * tallax/_src/bitonic_top_k.py:390-401 (bitonic_top_k).                             */
+#define TLX_TOPK_MAX_K 2048
+size_t tlx_top_k_workspace_bytes(int64_t rows, int64_t n, int k_max);
+int tlx_top_k(void* stream, const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride,
+              int k_max, const int32_t* k_per_row, int use_replace, double replace_val, int mode,
+              void* out_vals, int32_t* out_idx, int32_t* out_valid, int32_t* out_depths,
+              void* out_cutoff, void* workspace, size_t workspace_bytes);
+
+/* ---- counter-based noise -------------------------------------------------------
+ * out[i] = max(minval, f * (maxval - minval) + minval), f the [0,1) float made from
+ * x0^x1 of threefry2x32(key, (0, idx0[i]*dim1_size + idx1[i])).
+ * Replaces tallax/_src/sparse_random.py:43-64.                                      */
+int tlx_sparse_random_uniform(void* stream, uint32_t key0, uint32_t key1, const int32_t* idx0,
+                              const int32_t* idx1, int64_t count, int64_t dim1_size, float minval,
+                              float maxval, float* out);
+
+/* ---- top-p mask ------------------------------------------------------------------
+ * topk_logits, out: f32 [k, batch], column b sorted descending along axis 0; p: f32[batch].
+ * Keeps entries >= the logit at index #(cumulative softmax mass < p) (0.0 if that index
+ * is k, as the reference's out-of-range gather gives), others become replace_val.
+ * Replaces tallax/_src/sampling.py:25-62 (top_p_mask inside the fused kernel).      */
+int tlx_top_p_mask(void* stream, const float* topk_logits, const float* p, int k, int64_t batch,
+                   double replace_val, float* out);
+
+/* ---- Gumbel arg-max with indexed noise -----------------------------------------
+ * logits f32 [rows, cols]; noise at element e is the threefry uniform (clamped to
+ * [tiny, 1)) with counter idx0[e] * dim1_size + idx1[e].  out_pos[line] = position along
+ * `axis` of max(logits - log(-log(u))), lower position on ties; one line per row
+ * (axis 1) or per column (axis 0).
+ * Replaces tallax/_src/sparse_random.py:68-94 (sparse_random_categorical).          */
+int tlx_gumbel_argmax(void* stream, const float* logits, const int32_t* idx0, const int32_t* idx1,
+                      int64_t rows, int64_t cols, uint32_t key0, uint32_t key1, int64_t dim1_size,
+                      int axis, int32_t* out_pos);
+
+/* ---- candidate-level sampler ---------------------------------------------------
+ * topk_logits [rows, k] (F32 or BF16) sorted descending with masked positions equal to
+ * replace_val, topk_idx [rows, k] int32.  Top-p mask on unscaled logits, divide by
+ * temperature, Gumbel noise, arg-max, greedy when temperature < 1e-5.
+ * Noise: `noise` (nullable) is the dense uniform tensor [*, noise_stride] read at
+ * (row + dim0_offset, token); if NULL the threefry key (key0, key1) is used with
+ * counter (row + dim0_offset) * vocab_size + token.
+ * Replaces tallax/_src/sampling.py:185-208 (_top_p_and_sample).                     */
+int tlx_top_p_and_sample(void* stream, const void* topk_logits, int dtype, const int32_t* topk_idx,
+                         int64_t rows, int k, const float* top_p, const float* temperature,
+                         const float* noise, int64_t noise_stride, uint32_t key0, uint32_t key1,
+                         int64_t vocab_size, double replace_val, int64_t dim0_offset,
+                         int32_t* out_tokens);
+
+/* ---- fused sampler -------------------------------------------------------------
+ * logits [rows, vocab] (F32 or BF16, row stride in elements) -> token ids int32[rows]
+ * in one call: per-row top-k (0 or >= vocab disables it), top-p, temperature,
+ * Gumbel noise (dense tensor or threefry key as above), greedy override.
+ * out_status (nullable, device int32[rows]): bit 0 = general path used, bit 1 = a bounded
+ * wait gave up (result invalid).
+ * Replaces the whole of tallax/_src/sampling.py:331-343 (`sample`), i.e. the
+ * top_dynamic_k kernel (top_k.py:482-506) followed by _top_p_and_sample.            */
+size_t tlx_sample_workspace_bytes(int64_t rows, int64_t vocab);
+int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab,
+               int64_t row_stride, const int32_t* top_k, const float* top_p,
+               const float* temperature, const float* noise, int64_t noise_stride, uint32_t key0,
+               uint32_t key1, int64_t dim0_offset, int32_t* out_tokens, int32_t* out_status,
+               void* workspace, size_t workspace_bytes);
+
+/* ---- vocab-sharded sampler -----------------------------------------------------
+ * Stage 1, on each shard: the shard's top-`k_cand` as (f32 value, GLOBAL token id =
+ * local column + col_offset, uniform noise at that token), each [rows, k_cand].
+ * `noise` is the shard's slice [rows, v_local] (stride in elements) or NULL for the
+ * threefry key with counter (row + dim0_offset) * vocab_total + global token.
+ * Stage 2, after the candidates of all shards were gathered: candidate i of row r is read
+ * at (i / k_per_block) * block_stride + r * row_stride + (i % k_per_block) in each of the
+ * three arrays (a plain [rows, n_cand] layout is k_per_block = row_stride = n_cand,
+ * block_stride = 0; the output of an all-gather of per-shard [rows, k] blocks is
+ * k_per_block = row_stride = k, block_stride = the distance between shards' blocks).
+ * Blocks must be in ascending token order.  Merge by (value desc, token asc), keep
+ * top_k[row] (<= 0 keeps all candidates), then the sampler tail.
+ * Replaces the shard-mapped body of tallax/_src/sampling.py:305-320.                */
+size_t tlx_shard_candidates_workspace_bytes(int64_t rows, int64_t v_local, int k_cand);
+int tlx_shard_candidates(void* stream, const void* logits, int dtype, int64_t rows, int64_t v_local,
+                         int64_t row_stride, int64_t col_offset, int k_cand, const float* noise,
+                         int64_t noise_stride, uint32_t key0, uint32_t key1, int64_t vocab_total,
+                         int64_t dim0_offset, float* out_vals, int32_t* out_idx, float* out_noise,
+                         void* workspace, size_t workspace_bytes);
+int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* cand_idx,
+                         const float* cand_noise, int64_t rows, int n_cand, int k_per_block,
+                         int64_t block_stride, int64_t row_stride, const int32_t* top_k,
+                         const float* top_p, const float* temperature, int32_t* out_tokens);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TALLAX_B200_H_ */

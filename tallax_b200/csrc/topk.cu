@@ -1,0 +1,182 @@
+// Row-wise exact / single-pass top-k and the per-shard candidate stage of the
+// vocab-sharded sampler.  One CTA per row: the streaming collector leaves a superset of
+// the top-k in shared memory, a bitonic network orders it by (value desc, index asc).
+#include "select.cuh"
+
+namespace tlx {
+
+constexpr int kTopkThreads = 512;
+
+struct TopkParams {
+  const void* x;
+  int64_t rows, n, row_stride;
+  int k_max;
+  const int32_t* k_per_row;
+  int use_replace;
+  double replace_val;
+  int mode;
+  void* out_vals;
+  int32_t* out_idx;
+  int32_t* out_valid;
+  int32_t* out_depths;
+  void* out_cutoff;
+  // candidate stage of the vocab-sharded sampler (all null / zero for plain top-k)
+  float* cand_vals;
+  int32_t* cand_idx;
+  float* cand_noise;
+  int64_t col_offset;
+  int64_t dim0_offset;
+  NoiseSrc noise;
+};
+
+template <int DT>
+__device__ __forceinline__ typename Elem<DT>::type cast_replace(double v) {
+  if constexpr (DT == TLX_F32) return (float)v;
+  else if constexpr (DT == TLX_BF16) return __float2bfloat16_rn((float)v);
+  else if constexpr (DT == TLX_F16) return __float2half_rn((float)v);
+  else if constexpr (DT == TLX_I32) return (int32_t)v;
+  else return (uint32_t)v;
+}
+
+template <int DT, int CAP>
+__global__ void __launch_bounds__(kTopkThreads) topk_kernel(TopkParams p) {
+  using T = typename Elem<DT>::type;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
+  uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
+  const int64_t r = blockIdx.x;
+  const T* row = reinterpret_cast<const T*>(p.x) + r * p.row_stride;
+  const int K = p.k_max;
+
+  bool ok = collect_row<DT, CAP>(row, p.n, K, s, cand);
+  if (!ok) {
+    if (p.mode == 0) {
+      exact_select_row<DT>(row, p.n, K, s, cand);
+    } else {
+      if (threadIdx.x == 0) { if (p.out_valid) atomicExch(p.out_valid, 0); s.fill = CAP; }
+      __syncthreads();
+    }
+  }
+  const int m = min(s.fill, CAP);
+  sort_candidates(cand, m);
+
+  const int k_row = p.k_per_row ? p.k_per_row[r] : K;
+  for (int j = threadIdx.x; j < K; j += blockDim.x) {
+    const uint64_t c = cand[j];
+    const int32_t col = (int32_t)cand_low(c);
+    const bool have = j < m;
+    if (p.cand_vals) {
+      // candidate stage: f32 value, global token id, noise at that token
+      const float v = have ? elem_as_float<DT>(row[col]) : -INFINITY;
+      const int64_t tok = (int64_t)col + p.col_offset;
+      p.cand_vals[r * K + j] = v;
+      p.cand_idx[r * K + j] = have ? (int32_t)tok : -1;
+      float u = 0.5f;
+      if (have) u = p.noise.dense ? __ldg(p.noise.dense + r * p.noise.stride + col) : p.noise.at(r + p.dim0_offset, tok);
+      p.cand_noise[r * K + j] = u;
+    } else {
+      T v = have ? row[col] : cast_replace<DT>(0.0);
+      if (p.use_replace && j >= k_row) v = cast_replace<DT>(p.replace_val);
+      reinterpret_cast<T*>(p.out_vals)[r * K + j] = v;
+      p.out_idx[r * K + j] = have ? col : 0;
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (p.out_depths) p.out_depths[r] = s.refinements;
+    if (p.out_cutoff) {
+      if constexpr (DT == TLX_I32 || DT == TLX_U32)
+        reinterpret_cast<int32_t*>(p.out_cutoff)[r] = (int32_t)Elem<TLX_I32>::from_key((uint32_t)s.bin << kHistShift);
+      else
+        reinterpret_cast<float*>(p.out_cutoff)[r] = bin_lower_value(s.bin);
+    }
+  }
+}
+
+__global__ void set_int_kernel(int32_t* p, int32_t v) { *p = v; }
+
+template <int DT, int CAP>
+static int launch_topk_cap(cudaStream_t st, const TopkParams& p) {
+  const size_t smem = ((sizeof(SelectShared) + 15) & ~size_t(15)) + (size_t)CAP * 8;
+  static bool configured = false;  // per (DT, CAP) instantiation; idempotent, so a race is harmless
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(topk_kernel<DT, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "top_k: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  if (p.out_valid) set_int_kernel<<<1, 1, 0, st>>>(p.out_valid, 1);
+  topk_kernel<DT, CAP><<<(unsigned)p.rows, kTopkThreads, smem, st>>>(p);
+  TLX_CHECK_LAUNCH("top_k");
+  return TLX_OK;
+}
+
+template <int DT>
+static int launch_topk(cudaStream_t st, const TopkParams& p) {
+  if (p.k_max <= 256) return launch_topk_cap<DT, 1024>(st, p);
+  if (p.k_max <= 1024) return launch_topk_cap<DT, 4096>(st, p);
+  return launch_topk_cap<DT, 8192>(st, p);
+}
+
+static int dispatch_topk(cudaStream_t st, int dtype, const TopkParams& p, const char* what) {
+  switch (dtype) {
+    case TLX_F32: return launch_topk<TLX_F32>(st, p);
+    case TLX_BF16: return launch_topk<TLX_BF16>(st, p);
+    case TLX_F16: return launch_topk<TLX_F16>(st, p);
+    case TLX_I32: return launch_topk<TLX_I32>(st, p);
+    case TLX_U32: return launch_topk<TLX_U32>(st, p);
+    default: return set_error(TLX_ERR_UNSUPPORTED, "%s: dtype %d not supported", what, dtype);
+  }
+}
+
+}  // namespace tlx
+
+using namespace tlx;
+
+extern "C" {
+
+size_t tlx_top_k_workspace_bytes(int64_t, int64_t, int) { return 0; }
+
+int tlx_top_k(void* stream, const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int k_max,
+              const int32_t* k_per_row, int use_replace, double replace_val, int mode, void* out_vals,
+              int32_t* out_idx, int32_t* out_valid, int32_t* out_depths, void* out_cutoff, void*, size_t) {
+  cudaStream_t st = (cudaStream_t)stream;
+  TLX_CHECK_ARG(rows >= 0 && n >= 0, "top_k: negative extent");
+  TLX_CHECK_ARG(k_max >= 1, "top_k: k must be >= 1, got %d", k_max);
+  if (k_max > TLX_TOPK_MAX_K)
+    return set_error(TLX_ERR_UNSUPPORTED, "top_k: k=%d exceeds the supported maximum %d", k_max, TLX_TOPK_MAX_K);
+  TLX_CHECK_ARG((int64_t)k_max <= n, "top_k: k=%d exceeds the row length %lld", k_max, (long long)n);
+  TLX_CHECK_ARG(mode == 0 || mode == 1, "top_k: mode must be 0 or 1");
+  TLX_CHECK_ARG(n < (1ll << 31) && rows < (1ll << 31), "top_k: extent too large");
+  TLX_CHECK_ARG(row_stride >= n, "top_k: row stride smaller than the row");
+  if (rows == 0) return TLX_OK;
+  TLX_CHECK_ARG(x && out_vals && out_idx, "top_k: null pointer");
+  TopkParams p{};
+  p.x = x; p.rows = rows; p.n = n; p.row_stride = row_stride; p.k_max = k_max; p.k_per_row = k_per_row;
+  p.use_replace = use_replace; p.replace_val = replace_val; p.mode = mode; p.out_vals = out_vals;
+  p.out_idx = out_idx; p.out_valid = out_valid; p.out_depths = out_depths; p.out_cutoff = out_cutoff;
+  return dispatch_topk(st, dtype, p, "top_k");
+}
+
+size_t tlx_shard_candidates_workspace_bytes(int64_t, int64_t, int) { return 0; }
+
+int tlx_shard_candidates(void* stream, const void* logits, int dtype, int64_t rows, int64_t v_local,
+                         int64_t row_stride, int64_t col_offset, int k_cand, const float* noise, int64_t noise_stride,
+                         uint32_t key0, uint32_t key1, int64_t vocab_total, int64_t dim0_offset, float* out_vals,
+                         int32_t* out_idx, float* out_noise, void*, size_t) {
+  cudaStream_t st = (cudaStream_t)stream;
+  TLX_CHECK_ARG(rows >= 0 && v_local > 0, "shard_candidates: bad extent");
+  TLX_CHECK_ARG(k_cand >= 1 && k_cand <= 1024, "shard_candidates: k_cand must be in [1, 1024], got %d", k_cand);
+  TLX_CHECK_ARG((int64_t)k_cand <= v_local, "shard_candidates: k_cand exceeds the shard width");
+  TLX_CHECK_ARG(dtype == TLX_F32 || dtype == TLX_BF16 || dtype == TLX_F16, "shard_candidates: float logits only");
+  TLX_CHECK_ARG(row_stride >= v_local, "shard_candidates: row stride smaller than the row");
+  TLX_CHECK_ARG(col_offset >= 0 && col_offset + v_local <= (1ll << 31), "shard_candidates: token ids exceed int32");
+  if (rows == 0) return TLX_OK;
+  TLX_CHECK_ARG(logits && out_vals && out_idx && out_noise, "shard_candidates: null pointer");
+  TopkParams p{};
+  p.x = logits; p.rows = rows; p.n = v_local; p.row_stride = row_stride; p.k_max = k_cand;
+  p.cand_vals = out_vals; p.cand_idx = out_idx; p.cand_noise = out_noise; p.col_offset = col_offset;
+  p.dim0_offset = dim0_offset;
+  p.noise.dense = noise; p.noise.stride = noise_stride; p.noise.k0 = key0; p.noise.k1 = key1; p.noise.vocab = vocab_total;
+  return dispatch_topk(st, dtype, p, "shard_candidates");
+}
+
+}  // extern "C"

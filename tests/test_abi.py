@@ -1,0 +1,72 @@
+"""CPU checks of the drop-in boundary: the library loads and exports every declared symbol."""
+import os
+import re
+
+from tallax_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "tallax_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tlx_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_builds_and_loads():
+    build.build()
+    lib = _lib.load()
+    assert lib.tlx_abi_version() == 1
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = _lib.load()
+    names = _declared()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+
+
+def test_argument_errors_need_no_gpu():
+    lib = _lib.load()
+    # bad axis is rejected before any CUDA call
+    rc = lib.tlx_cumsum(None, None, None, 4, 4, _lib.TLX_F32, 2, 0)
+    assert rc == _lib.TLX_ERR_INVALID
+    assert b"axis" in lib.tlx_last_error()
+    rc = lib.tlx_top_k(None, None, _lib.TLX_F32, 4, 100, 100, 4096, None, 0, 0.0, 0, None, None, None, None, None,
+                       None, 0)
+    assert rc == _lib.TLX_ERR_UNSUPPORTED
+    assert lib.tlx_sort_workspace_bytes(128, 65536) == 128 * 65536 * 8
+    assert lib.tlx_sort_workspace_bytes(16, 2048) == 0
+    assert lib.tlx_sample_workspace_bytes(256, 128256) == 257 * 4
+
+
+def test_python_mirror_error_behaviour():
+    import pytest
+    import torch
+
+    from tallax_b200 import tax, tumpy
+    from tallax_b200._src.bitonic_top_k import bitonic_top_k
+    from tallax_b200._src.sampling import top_p_mask
+
+    a = torch.zeros(2, 2, 16)
+    with pytest.raises(ValueError):
+        tumpy.sort(a, axis=0)
+    with pytest.raises(ValueError):
+        tax.sort([torch.zeros(2, 4), torch.zeros(2, 5)], num_keys=1)
+    with pytest.raises(ValueError):
+        tax.sort(torch.zeros(4), num_keys=1)
+    with pytest.raises(ValueError):
+        bitonic_top_k(torch.zeros(8, 256), k=256)
+    with pytest.raises(NotImplementedError):
+        bitonic_top_k(torch.zeros(8, 256), k=128, descending=False)
+    with pytest.raises(ValueError):
+        tax.top_k(torch.zeros(7, 256), 4)  # num_tokens not divisible by block_token
+    with pytest.raises(NotImplementedError):
+        tax.top_dynamic_k(torch.zeros(8, 8192), k=4, max_k=4096)
+    with pytest.raises(NotImplementedError):
+        top_p_mask(topk_logits=torch.zeros(4, 4), p=torch.zeros(4), replace_val=0.0, axis=1)
+    with pytest.raises(ValueError):
+        tax.cumsum(torch.zeros(4, 4), axis=0)  # CPU tensor: there is no CPU path

@@ -1,0 +1,102 @@
+"""GPU parity: exact / single-pass / multi-operand top-k against the oracle, bit-exact with ties to the lower index."""
+import numpy as np
+import pytest
+
+from oracle import tallax_oracle as o
+from tallax_b200 import tax
+from tallax_b200._src.bitonic_top_k import bitonic_top_k
+from tests.conftest import exact_match, to_dev, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_topk(cuda, x, k):
+    v, i = tax.top_k(to_dev(x, cuda), k, block_token=1)
+    ev, ei = o.top_k(x, k)
+    assert np.array_equal(to_np(i), ei)
+    assert exact_match(to_np(v), ev)
+
+
+@pytest.mark.parametrize("shape", [(8, 128), (16, 256), (13, 167), (256, 256), (173, 195)])
+@pytest.mark.parametrize("dtype", ["f32", "i32"])
+def test_bitonic_topk_shapes(cuda, shape, dtype):
+    rng = np.random.default_rng(0)
+    arr = rng.standard_normal(shape).astype(np.float32) if dtype == "f32" else rng.integers(0, 1000, shape).astype(
+        np.int32)
+    idx = np.broadcast_to(np.arange(shape[1], dtype=np.int32), shape).copy()
+    k = min(128, shape[1])
+    v, i = bitonic_top_k([to_dev(arr, cuda), to_dev(idx, cuda)], k=k, num_keys=1, descending=True)
+    ev, ei = o.bitonic_top_k([arr, idx], k=k, num_keys=1)
+    assert exact_match(to_np(v), ev) and np.array_equal(to_np(i), ei)
+
+
+def test_topk_config_f32(cuda):
+    # benchmark configuration 1: f32 [8, 32768], k=64
+    x = np.random.Generator(np.random.Philox(0)).standard_normal((8, 32768), dtype=np.float32)
+    _check_topk(cuda, x, 64)
+
+
+def test_topk_bf16_wide(cuda):
+    # the reference's own top-k test shape: bf16 [16, 201088], k=64
+    x = np.random.default_rng(0).standard_normal((16, 201088)).astype(np.float32).astype(o.bfloat16)
+    _check_topk(cuda, x, 64)
+
+
+@pytest.mark.parametrize("k", [1, 7, 128, 129, 1000, 2048])
+@pytest.mark.parametrize("n", [2048, 50000])
+def test_topk_k_range(cuda, k, n):
+    x = np.random.default_rng(k).standard_normal((5, n)).astype(np.float32)
+    _check_topk(cuda, x, k)
+
+
+@pytest.mark.parametrize("kind", ["ascending", "descending", "constant", "two_values", "int_ties", "neg_inf_masked",
+                                  "nan_and_zero"])
+def test_topk_adversarial_rows(cuda, kind):
+    n, k = 40000, 100
+    rng = np.random.default_rng(3)
+    if kind == "ascending":  # every element beats the running threshold: candidate overflow -> radix fallback
+        x = np.tile(np.arange(n, dtype=np.float32), (3, 1))
+    elif kind == "descending":
+        x = np.tile(np.arange(n, 0, -1).astype(np.float32), (3, 1))
+    elif kind == "constant":  # one huge tie group: the k lowest indices win
+        x = np.full((3, n), 1.5, np.float32)
+    elif kind == "two_values":
+        x = rng.integers(0, 2, (3, n)).astype(np.float32)
+    elif kind == "int_ties":
+        x = rng.integers(0, 1000, (3, n)).astype(np.int32)
+    elif kind == "neg_inf_masked":  # logits with most of the vocabulary masked out
+        x = rng.standard_normal((3, n)).astype(np.float32)
+        x[:, rng.random(n) < 0.999] = -np.inf
+    else:
+        x = rng.standard_normal((3, n)).astype(np.float32)
+        x[:, ::7] = 0.0
+        x[:, 3::7] = -0.0
+        x[0, 5] = np.nan
+    _check_topk(cuda, x, k)
+
+
+def test_top_dynamic_k_masks_with_replace_val(cuda):
+    x = np.random.default_rng(1).standard_normal((16, 30000)).astype(np.float32)
+    k = np.random.default_rng(2).integers(1, 129, 16).astype(np.int32)
+    v, i = tax.top_dynamic_k(to_dev(x, cuda), to_dev(k, cuda), max_k=128, guarantee_convergence=True,
+                             replace_val=-1e12)
+    ev, ei = o.top_dynamic_k(x, k, 128, replace_val=-1e12)
+    assert np.array_equal(to_np(v), ev) and np.array_equal(to_np(i), ei)
+
+
+def test_single_pass_topk_contract(cuda):
+    # guarantee_convergence=False: five outputs; iid rows are answered exactly (valid), recall 1.0
+    x = np.random.Generator(np.random.Philox(3)).standard_normal((64, 262144), dtype=np.float32)
+    v, i, valid, depths, cutoff = tax.top_dynamic_k(to_dev(x, cuda), 128, max_k=128, guarantee_convergence=False)
+    ev, ei = o.top_k(x, 128)
+    assert bool(valid)
+    assert o.topk_recall(to_np(i), ei) >= 0.95
+    assert np.array_equal(to_np(i), ei) and np.array_equal(to_np(v), ev)
+    assert depths.shape == (64,) and cutoff.shape == (64,)
+    assert np.all(to_np(cutoff) <= ev[:, -1])  # the reported pivot is a lower bound of the k-th value
+    # an ascending row defeats the single pass: valid is cleared, the answer is still k in-range distinct indices
+    bad = np.tile(np.arange(100000, dtype=np.float32), (8, 1))
+    v, i, valid, _, _ = tax.top_dynamic_k(to_dev(bad, cuda), 64, max_k=64, guarantee_convergence=False)
+    assert not bool(valid)
+    ii = to_np(i)
+    assert ii.min() >= 0 and ii.max() < 100000 and all(len(set(r.tolist())) == 64 for r in ii)
