@@ -12,6 +12,8 @@
 //                    count * exp(value - max), so counts alone give the exact top-p
 //                    threshold); f32 rows use 12/12/8-bit radix passes with f64 mass bins.
 //                    Both end with a streaming Gumbel arg-max over the kept elements.
+#include <mutex>
+
 #include "select.cuh"
 
 namespace tlx {
@@ -146,28 +148,22 @@ __device__ __forceinline__ double stream_mass(const typename Elem<DT>::type* __r
 
 // Streaming Gumbel arg-max over the kept elements:
 //   key >= vstar, and inside the top-k set: key > vk, or key == vk with tie rank < ties_admitted
-// (rank = number of equal keys at lower columns).  `ordered` selects the variant that
+// (rank = number of equal keys at lower columns).  `ordered` selects the traversal that
 // tracks tie ranks; it is only needed when the kept set cuts through the tie group.
-template <int DT>
-__device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n, float T_,
-                                            uint32_t vstar, bool bounded, uint32_t vk, uint32_t ties_admitted,
-                                            bool ordered, const NoiseSrc& noise, int64_t nrow, SelectShared& s) {
+//
+// The score y = x / T + gumbel(u) is screened in f32: every thread keeps its two best
+// screened scores, the block maximum A is reduced, and only elements within kGumbelSlack
+// of A are decided on the f64-evaluated Gumbel term.  If some thread has two elements that
+// close to A (there may then be a third), the row is traversed once more instead.
+template <int DT, typename F>
+__device__ __forceinline__ void for_each_kept(const typename Elem<DT>::type* __restrict__ row, int64_t n,
+                                              uint32_t vstar, bool bounded, uint32_t vk, uint32_t ties_admitted,
+                                              bool ordered, SelectShared& s, F&& f) {
   using T = typename Elem<DT>::type;
-  Best best{-INFINITY, 0x7FFFFFFF};
-  auto consider = [&](T v, int64_t c) {
-    const float x = elem_as_float<DT>(v);
-    const float u = noise.at(nrow, c);
-    const float q = __fdiv_rn(x, T_);
-    const float a = q + gumbel_fast(u);
-    if (a >= best.y - (kGumbelSlack + 1e-5f * fabsf(best.y)) || best.y == -INFINITY) {
-      Best cnd{q + gumbel_exact(u), (int)c};
-      best = best_of(best, cnd);
-    }
-  };
   if (!ordered) {
     for_each_elem<DT>(row, 0, n, [&](T v, int64_t c) {
       const uint32_t key = Elem<DT>::key(v);
-      if (key >= vstar && (!bounded || key >= vk)) consider(v, c);
+      if (key >= vstar && (!bounded || key >= vk)) f(elem_as_float<DT>(v), c);
     });
   } else {
     const int64_t L = (n + blockDim.x - 1) / blockDim.x;
@@ -179,10 +175,13 @@ __device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __res
     for (int64_t c = b0; c < b1; ++c) {
       const T v = row[c];
       const uint32_t key = Elem<DT>::key(v);
-      if (key > vk) { if (key >= vstar) consider(v, c); }
-      else if (key == vk) { if (rank < ties_admitted && key >= vstar) consider(v, c); rank++; }
+      if (key > vk) { if (key >= vstar) f(elem_as_float<DT>(v), c); }
+      else if (key == vk) { if (rank < ties_admitted && key >= vstar) f(elem_as_float<DT>(v), c); rank++; }
     }
   }
+}
+
+__device__ __forceinline__ Best block_best(Best best, SelectShared& s) {
   best = warp_best(best);
   __syncthreads();
   if (lane_id() == 0) { s.scan_f64[warp_id()] = (double)best.y; s.scan_u32[warp_id()] = (uint32_t)best.tok; }
@@ -191,7 +190,37 @@ __device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __res
   Best b{-INFINITY, 0x7FFFFFFF};
   for (int w = 0; w < nw; ++w) b = best_of(b, Best{(float)s.scan_f64[w], (int)s.scan_u32[w]});
   __syncthreads();
-  return b.tok;
+  return b;
+}
+
+template <int DT>
+__device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n, float T_,
+                                            uint32_t vstar, bool bounded, uint32_t vk, uint32_t ties_admitted,
+                                            bool ordered, const NoiseSrc& noise, int64_t nrow, SelectShared& s) {
+  // screening pass: two best screened scores per thread, with what is needed to re-evaluate the best
+  float a1 = -INFINITY, a2 = -INFINITY, q1 = 0.f, u1 = 0.5f;
+  int c1 = 0x7FFFFFFF;
+  for_each_kept<DT>(row, n, vstar, bounded, vk, ties_admitted, ordered, s, [&](float x, int64_t c) {
+    const float u = noise.at(nrow, c);
+    const float q = __fdiv_rn(x, T_);
+    const float a = q + gumbel_fast(u);
+    if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = u; c1 = (int)c; }
+    else if (a > a2) a2 = a;
+  });
+  const Best top = block_best(Best{a1, c1}, s);
+  const float cut = top.y - (kGumbelSlack + 1e-5f * fabsf(top.y));
+  const int crowded = __syncthreads_or(a2 >= cut);
+  Best best{-INFINITY, 0x7FFFFFFF};
+  if (!crowded) {
+    if (a1 >= cut) best = Best{q1 + gumbel_exact(u1), c1};
+  } else {
+    for_each_kept<DT>(row, n, vstar, bounded, vk, ties_admitted, ordered, s, [&](float x, int64_t c) {
+      const float u = noise.at(nrow, c);
+      const float q = __fdiv_rn(x, T_);
+      if (q + gumbel_fast(u) >= cut) best = best_of(best, Best{q + gumbel_exact(u), (int)c});
+    });
+  }
+  return block_best(best, s).tok;
 }
 
 // ---- bf16: 16-bit keys ---------------------------------------------------------------
@@ -275,7 +304,7 @@ __global__ void __launch_bounds__(kGenThreads) sample_general_bf16_kernel(Sample
 
     // ---- phase B: softmax denominator over the top-k set -------------------------------
     double Z = stream_mass<TLX_BF16>(row, n, xmax, bounded, vk32, s);
-    if (bounded) Z += (double)ties_admitted * exp((double)key_f32(vk32) - (double)xmax);
+    if (bounded) Z += (double)ties_admitted * (double)expf(key_f32(vk32) - xmax);
     const double target = target_frac * Z;
 
     // ---- phase C: top-p threshold = first value group (descending) whose cumulative mass
@@ -292,7 +321,7 @@ __global__ void __launch_bounds__(kGenThreads) sample_general_bf16_kernel(Sample
           const int k16 = whi - (i0 + j);
           uint32_t c = win[i0 + j];
           if (bounded) { if (k16 < vk16) c = 0; else if (k16 == vk16) c = ties_admitted; }
-          if (c && k16 >= 0) local += (double)c * exp((double)key_f32(key16_to_key32((uint32_t)k16)) - (double)xmax);
+          if (c && k16 >= 0) local += (double)c * (double)expf(key_f32(key16_to_key32((uint32_t)k16)) - xmax);
         }
         double total;
         const double incl = block_scan_incl<double>(local, s.scan_f64, &total, ShflUpF64());
@@ -306,7 +335,7 @@ __global__ void __launch_bounds__(kGenThreads) sample_general_bf16_kernel(Sample
             uint32_t c = win[i0 + j];
             if (bounded) { if (k16 < vk16) c = 0; else if (k16 == vk16) c = ties_admitted; }
             if (c && k16 >= 0) {
-              run += (double)c * exp((double)key_f32(key16_to_key32((uint32_t)k16)) - (double)xmax);
+              run += (double)c * (double)expf(key_f32(key16_to_key32((uint32_t)k16)) - xmax);
               if (run >= target) { s.tmp_i[3] = k16; break; }
             }
           }
@@ -597,9 +626,20 @@ __global__ void __launch_bounds__(256) gumbel_argmax_kernel(const float* __restr
   }
 }
 
+// Raises a kernel's dynamic shared memory limit once per (kernel, device).
 static int ensure_smem(const void* func, size_t bytes, const char* what) {
+  struct Entry { const void* func; int dev; size_t bytes; };
+  static Entry cache[256];
+  static int used = 0;
+  static std::mutex mu;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < used; ++i)
+    if (cache[i].func == func && cache[i].dev == dev && cache[i].bytes >= bytes) return TLX_OK;
   cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "%s: cudaFuncSetAttribute(%zu): %s", what, bytes, cudaGetErrorString(e));
+  if (used < 256) cache[used++] = Entry{func, dev, bytes};
   return TLX_OK;
 }
 

@@ -41,7 +41,8 @@ struct SelectShared {
 // Real value at the lower edge of histogram bin b, clamped so that it is never a NaN
 // pattern: a float compare against it passes a superset of "bin >= b".
 __device__ __forceinline__ float bin_lower_value(int b) {
-  b = max(8, min(b, 4088));
+  if (b <= 7) return -INFINITY;  // -inf itself lives in bin 7
+  b = min(b, 4088);
   return key_f32((uint32_t)b << kHistShift);
 }
 

@@ -97,12 +97,8 @@ __global__ void set_int_kernel(int32_t* p, int32_t v) { *p = v; }
 template <int DT, int CAP>
 static int launch_topk_cap(cudaStream_t st, const TopkParams& p) {
   const size_t smem = ((sizeof(SelectShared) + 15) & ~size_t(15)) + (size_t)CAP * 8;
-  static bool configured = false;  // per (DT, CAP) instantiation; idempotent, so a race is harmless
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(topk_kernel<DT, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "top_k: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured = true;
-  }
+  cudaError_t e = cudaFuncSetAttribute(topk_kernel<DT, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "top_k: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   if (p.out_valid) set_int_kernel<<<1, 1, 0, st>>>(p.out_valid, 1);
   topk_kernel<DT, CAP><<<(unsigned)p.rows, kTopkThreads, smem, st>>>(p);
   TLX_CHECK_LAUNCH("top_k");
