@@ -1,28 +1,80 @@
 // Fused temperature / top-k / top-p / noise sampler on [rows, vocab] logits, the
 // candidate-level sampler, and the merge stage of the vocab-sharded sampler.
 //
-// tlx_sample runs two kernels on the caller's stream:
-//   fast kernel    : one CTA per row.  Greedy rows need only an arg-max.  Rows with
-//                    1 <= top_k <= kFastK stream the row ONCE (collect_row), sort the few
-//                    candidates in shared memory and finish there (sample_tail).  Every
-//                    other row (top-k disabled or large, or a candidate overflow) is
-//                    appended to a work list in the workspace.
-//   general kernel : persistent CTAs drain the work list.  bf16 rows use a windowed
-//                    histogram over the full 16-bit key (softmax mass of a value group is
-//                    count * exp(value - max), so counts alone give the exact top-p
-//                    threshold); f32 rows use 12/12/8-bit radix passes with f64 mass bins.
-//                    Both end with a streaming Gumbel arg-max over the kept elements.
+// tlx_sample is ONE persistent kernel.  Every row is cut into S slices of interleaved
+// 4 KB chunks; the work items (row, slice) are handed out through an atomic counter and
+// each CTA keeps two slices in shared memory: the one it works on and the next one,
+// which a bulk copy (TMA, cp.async.bulk + mbarrier) is already bringing in.  Logits are
+// therefore read from HBM exactly once, by all SMs at the same rate, whatever the mix
+// of per-row parameters.
+//
+// A slice is reduced in shared memory to a small record in the workspace:
+//   greedy row (temperature < 1e-5)  : the slice's arg-max;
+//   1 <= top_k <= kFastK             : every element at or above a slice-local threshold
+//                                      bin (chosen from a sample so that about
+//                                      top_k / S + 6 sigma elements pass), plus that bin;
+//   top-k disabled or large, bf16    : slice maximum, histogram over the 8192 16-bit keys
+//                                      below it, and sum of exp(x - slice max).
+// The CTA that completes a row's last slice (atomic count, no waiting) merges the row:
+// candidates at or above the highest slice threshold are a superset of the row's top-k
+// if there are at least top_k of them (checked; otherwise the row is redone exactly from
+// global memory), they are sorted by (value desc, token asc) and the sampler tail runs.
+// Rows without top-k take the top-p threshold from the merged histogram and then stream
+// the row once more (from L2) for the Gumbel arg-max; those rows are scheduled first.
 #include <mutex>
 
-#include "select.cuh"
+#include "sampler_general.cuh"
 
 namespace tlx {
 
-constexpr int kFastThreads = 512;
-constexpr int kFastCap = 4096;
-constexpr int kFastK = 1024;       // largest top_k served by the single-pass kernel
-constexpr int kGenThreads = 1024;
-constexpr int kWindow = 32768;     // bf16 general path: full-key histogram window
+constexpr int kThreads = 256;        // slices kernel
+constexpr int kRowThreads = 512;     // merge kernel
+constexpr int kSliceBytes = 28672;   // one slice buffer (two per CTA)
+#ifdef TLX_CHUNK_BYTES
+constexpr int kChunkBytes = TLX_CHUNK_BYTES;
+#else
+constexpr int kChunkBytes = 4096;    // interleaving granule
+#endif
+constexpr int kChunksPerSlice = kSliceBytes / kChunkBytes;
+constexpr int kRecordCap = 2048;     // candidates (u64) a slice may publish == 16 KB payload
+constexpr int kMergeCap = 4096;      // candidates (u64) held in shared memory
+constexpr int kWin = 8192;           // bf16 histogram window (bins below the maximum key)
+constexpr int kFastK = 1024;         // largest top_k served by the candidate path
+constexpr int kSample = 2048;        // elements of a slice sampled for the first threshold
+constexpr int kPlanRows = 1024;      // rows up to this count are reordered (general rows first)
+constexpr int kMaxSlices = 256;
+constexpr uint32_t kWaitLimit = 1u << 24;  // bounded mbarrier polling
+
+enum RowClass : int { kGreedy = 0, kFast = 1, kGeneral = 2 };
+enum StatusBits : int { kStatusGeneral = 1, kStatusTimeout = 2, kStatusRedone = 4 };
+
+constexpr int kWarps = kThreads / 32;
+constexpr int kWarpCap = kRecordCap / kWarps;   // candidates one warp may publish per slice
+constexpr int kWarpHits = kSliceBytes / 16 / kWarps;   // vectors one warp owns in a slice
+static_assert(kWarps <= 16, "SliceHeader holds 16 per-warp counts");
+static_assert(kSliceBytes / 16 == kWarpHits * kWarps, "slice vectors must divide evenly among the warps");
+
+struct SliceHeader {   // 64 bytes, one per (row, slice) in the workspace
+  int cutoff_bin;      // candidates: every slice element with bin >= cutoff_bin was published
+  int overflow;        // candidates: a warp's segment overflowed, the set is incomplete
+  int kmax16;          // general/bf16: maximum 16-bit key of the slice
+  float smax;          // general/bf16: slice maximum as a float
+  unsigned long long top;  // greedy: arg-max composite (key << 32 | 0x7FFFFFFF - token)
+  double mass;         // general/bf16: sum of exp(x - slice max)
+  unsigned short wcount[16];  // candidates: entries in each warp's segment of the payload
+};
+static_assert(sizeof(SliceHeader) == 64, "SliceHeader layout");
+
+// What the warps of a CTA leave behind for the thread that publishes the slice.
+struct WarpResults {
+  unsigned long long top[kWarps];
+  unsigned short count[kWarps];
+  unsigned short bin[kWarps];
+  unsigned char overflow[kWarps];
+  int cutoff_bin;
+};
+
+constexpr size_t kRecordBytes = sizeof(SliceHeader) + (size_t)kRecordCap * 8;
 
 struct SampleParams {
   const void* logits;
@@ -34,179 +86,566 @@ struct SampleParams {
   int64_t dim0_offset;
   int32_t* out_tokens;
   int32_t* out_status;
-  int32_t* worklist;  // [0] = count, [1 ..] = row ids
+  // geometry
+  int S;               // slices per row
+  int chunk_elems;     // elements per chunk
+  int nchunks;         // chunks per row (the last one may be partial)
+  int use_tma;         // row starts and strides are 16-byte aligned
+  unsigned long long div_magic;  // ceil(2^40 / S)
+  // workspace
+  int32_t* counters;   // [1] set if a bounded wait gave up
+  unsigned char* records;
 };
 
-__device__ __forceinline__ void block_max_u64(uint64_t& v, SelectShared& s) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    uint64_t n = shfl_xor_u64(v, o);
-    v = n > v ? n : v;
+struct __align__(16) Control {   // per-CTA bookkeeping in shared memory
+  unsigned long long mbar[2];
+  int item[2];
+  int merge_flag[2];
+  int timeout;
+  int pad;
+  WarpResults wr[2];
+  unsigned short order[kPlanRows];  // planned row order (general rows first)
+  unsigned short kk[kPlanRows];     // per row: top-k (fast rows), 0xFFFE greedy, 0xFFFF general
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false if the barrier did not complete within kWaitLimit polls.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, uint32_t bytes,
+                                          unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// Release / acquire fence at GPU scope: orders this thread's (and, through a preceding barrier,
+// its CTA's) writes before a following atomic, without the total order __threadfence() asks for.
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- slice geometry ---------------------------------------------------------------------
+// Slice `sl` of a row owns the chunks sl, sl + S, sl + 2S, ...; they sit back to back in the
+// slice buffer.  Only the row's last chunk can be partial, and it is then the last chunk
+// of its slice.
+struct Geometry {
+  int S, chunk_elems, nchunks;
+  int64_t n;
+  int chunk_shift;  // chunk_elems is a power of two
+  unsigned long long div_magic;  // ceil(2^40 / S): exact x / S for 0 <= x < 2^30, S <= 256
+  __device__ __forceinline__ int div_S(int x) const { return (int)(((unsigned long long)(uint32_t)x * div_magic) >> 40); }
+  __device__ __forceinline__ int slice_chunks(int sl) const { return sl < nchunks ? div_S(nchunks - 1 - sl) + 1 : 0; }
+  __device__ __forceinline__ int slice_elems(int sl) const {
+    const int c = slice_chunks(sl);
+    if (c == 0) return 0;
+    const int last = (c - 1) * S + sl;
+    const int64_t rest = n - (int64_t)last * chunk_elems;
+    return (c - 1) * chunk_elems + (int)(rest < chunk_elems ? rest : chunk_elems);
   }
-  __syncthreads();
-  if (lane_id() == 0) reinterpret_cast<uint64_t*>(s.scan_f64)[warp_id()] = v;
-  __syncthreads();
-  const int nw = (blockDim.x + 31) >> 5;
-  uint64_t m = 0;
-  for (int w = 0; w < nw; ++w) {
-    uint64_t x = reinterpret_cast<uint64_t*>(s.scan_f64)[w];
-    m = x > m ? x : m;
+  // local position in the slice buffer -> column of the row
+  __device__ __forceinline__ int64_t column(int sl, int q) const {
+    const int lc = q >> chunk_shift;
+    return ((int64_t)(lc * S + sl) << chunk_shift) + (q & (chunk_elems - 1));
   }
-  v = m;
-  __syncthreads();
+};
+
+// ---- bringing a slice into shared memory -------------------------------------------------
+// Issued by warp 0 only.  TMA mode: one bulk copy per chunk, completion counted on `bar`;
+// a ragged tail shorter than 16 bytes is copied with plain loads.  Otherwise (rows not
+// 16-byte aligned) the warp copies the slice element by element and arrives on the barrier
+// with a zero-byte expectation, so that waiting works the same way in both modes.
+template <int DT>
+__device__ __forceinline__ void issue_slice_load(const SampleParams& p, const Geometry& g, int64_t row, int sl,
+                                                 unsigned char* buf, unsigned long long* bar) {
+  using T = typename Elem<DT>::type;
+  const T* src = reinterpret_cast<const T*>(p.logits) + row * p.row_stride;
+  const int chunks = g.slice_chunks(sl);
+  const int elems = g.slice_elems(sl);
+  const int lane = lane_id();
+  if (p.use_tma) {
+    const uint32_t bytes = (uint32_t)elems * sizeof(T);
+    const uint32_t bulk_bytes = bytes & ~15u;
+    if (lane == 0) mbar_expect_tx(bar, bulk_bytes);
+    __syncwarp();
+    for (int lc = lane; lc < chunks; lc += 32) {
+      uint32_t sz = kChunkBytes;
+      if (lc == chunks - 1) sz = bulk_bytes - (uint32_t)lc * kChunkBytes;
+      if (sz) bulk_load(buf + (size_t)lc * kChunkBytes, src + (int64_t)(lc * g.S + sl) * g.chunk_elems, sz, bar);
+    }
+    // ragged tail of the row's last chunk (fewer than 16 bytes)
+    const int tail_first = (int)(bulk_bytes / sizeof(T));
+    for (int q = tail_first + lane; q < elems; q += 32) reinterpret_cast<T*>(buf)[q] = src[g.column(sl, q)];
+  } else {
+    for (int q = lane; q < elems; q += 32) reinterpret_cast<T*>(buf)[q] = src[g.column(sl, q)];
+    __syncwarp();
+    if (lane == 0) mbar_expect_tx(bar, 0);
+  }
 }
 
-// (max key, lowest column holding it) of a row, as key << 32 | (0x7FFFFFFF - column).
-template <int DT>
-__device__ __forceinline__ uint64_t row_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n,
-                                               SelectShared& s) {
+// Calls f(value, local position) for every element of a slice buffer, 16-byte loads.
+template <int DT, typename F>
+__device__ __forceinline__ void for_each_slice_elem(const unsigned char* buf, int elems, F&& f) {
   using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const uint4* vp = reinterpret_cast<const uint4*>(buf);
+  const int nvec = elems / VEC;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 v = vp[i];
+    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) f(e[j], i * VEC + j);
+  }
+  for (int q = nvec * VEC + threadIdx.x; q < elems; q += blockDim.x) f(reinterpret_cast<const T*>(buf)[q], q);
+}
+
+__device__ __forceinline__ SliceHeader* record_header(const SampleParams& p, int64_t row, int sl) {
+  return reinterpret_cast<SliceHeader*>(p.records + ((size_t)row * p.S + sl) * kRecordBytes);
+}
+__device__ __forceinline__ unsigned char* record_payload(const SampleParams& p, int64_t row, int sl) {
+  return p.records + ((size_t)row * p.S + sl) * kRecordBytes + sizeof(SliceHeader);
+}
+
+// ---- slice reducers -----------------------------------------------------------------------
+// The greedy and candidate reducers are warp-local: every warp works on the vectors its lanes
+// own (thread t owns the 16-byte vectors t, t + blockDim, ...) and leaves its result in the
+// Control block; no block-wide barrier is needed until the slice is published.
+__device__ __forceinline__ __nv_bfloat162 bf162_bits(uint32_t w) {
+  __nv_bfloat162 r;
+  memcpy(&r, &w, sizeof(r));
+  return r;
+}
+
+// Block-wide max / min of one u32 per thread: one redux per warp, one shared-memory round.
+__device__ __forceinline__ uint32_t block_max_u32(uint32_t v, uint32_t* scratch) {
+  v = __reduce_max_sync(0xFFFFFFFFu, v);
+  if (lane_id() == 0) scratch[warp_id()] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  uint32_t r = __reduce_max_sync(0xFFFFFFFFu, scratch[lane_id() < nw ? lane_id() : 0]);
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ uint32_t block_min_u32(uint32_t v, uint32_t* scratch) {
+  return ~block_max_u32(~v, scratch);
+}
+
+// Largest key among the thread's first `vecs` vectors of a slice (all of them when vecs is
+// large), 0 if it owns none.  bf16 uses packed NaN-propagating maxima; the key is only formed
+// once at the end.
+template <int DT>
+__device__ __forceinline__ uint32_t thread_max_key(const unsigned char* buf, int nvec, int vecs) {
+  using T = typename Elem<DT>::type;
+  const uint4* vp = reinterpret_cast<const uint4*>(buf);
+  if constexpr (DT == TLX_BF16) {
+    __nv_bfloat162 mx = __float2bfloat162_rn(-INFINITY);
+    bool any = false;
+    for (int j = 0, i = threadIdx.x; j < vecs && i < nvec; ++j, i += blockDim.x) {
+      const uint4 v = vp[i];
+      mx = __hmax2_nan(__hmax2_nan(mx, bf162_bits(v.x)),
+                       __hmax2_nan(bf162_bits(v.y), __hmax2_nan(bf162_bits(v.z), bf162_bits(v.w))));
+      any = true;
+    }
+    if (!any) return 0u;
+    const uint32_t kl = f32_key(__low2float(mx)), kh = f32_key(__high2float(mx));
+    return kl > kh ? kl : kh;
+  } else {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    uint32_t mk = 0;
+    for (int j = 0, i = threadIdx.x; j < vecs && i < nvec; ++j, i += blockDim.x) {
+      const uint4 v = vp[i];
+      T e[VEC];
+      memcpy(e, &v, sizeof(v));
+#pragma unroll
+      for (int t = 0; t < VEC; ++t) { const uint32_t k = Elem<DT>::key(e[t]); mk = k > mk ? k : mk; }
+    }
+    return mk;
+  }
+}
+
+template <int DT>
+__device__ __forceinline__ typename Elem<DT>::type slice_elem(const unsigned char* buf, int q) {
+  return reinterpret_cast<const typename Elem<DT>::type*>(buf)[q];
+}
+
+// Greedy row: this warp's arg-max as key << 32 | (0x7FFFFFFF - local position); positions
+// grow with the column inside a slice, so the lowest position is the lowest column.
+template <int DT>
+__device__ __forceinline__ void reduce_slice_greedy(const unsigned char* buf, int elems, WarpResults& wr) {
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int nvec = elems / VEC;
+  uint32_t tkey = thread_max_key<DT>(buf, nvec, 1 << 30);
+  for (int q = nvec * VEC + threadIdx.x; q < elems; q += blockDim.x) {   // ragged tail of the row's last slice
+    const uint32_t k = Elem<DT>::key(slice_elem<DT>(buf, q));
+    tkey = k > tkey ? k : tkey;
+  }
+  const uint32_t wkey = __reduce_max_sync(0xFFFFFFFFu, tkey);
+  uint32_t qmin = 0xFFFFFFFFu;
+  if (tkey == wkey) {   // only the lanes that hold the warp's maximum look for its first position
+    const uint4* vp = reinterpret_cast<const uint4*>(buf);
+    for (int i = threadIdx.x; i < nvec && qmin == 0xFFFFFFFFu; i += blockDim.x) {
+      bool here = true;
+      if constexpr (DT == TLX_BF16) {
+        if (wkey != 0xFFFFFFFFu) {   // packed equality screens the vector (-0 == +0, as in the key domain)
+          const uint4 v = vp[i];
+          const __nv_bfloat162 m2 = __float2bfloat162_rn(key_f32(wkey));
+          here = (__heq2_mask(bf162_bits(v.x), m2) | __heq2_mask(bf162_bits(v.y), m2) |
+                  __heq2_mask(bf162_bits(v.z), m2) | __heq2_mask(bf162_bits(v.w), m2)) != 0u;
+        }
+      }
+      if (here) {
+#pragma unroll
+        for (int t = VEC - 1; t >= 0; --t)
+          if (Elem<DT>::key(slice_elem<DT>(buf, i * VEC + t)) == wkey) qmin = (uint32_t)(i * VEC + t);
+      }
+    }
+    for (int q = nvec * VEC + threadIdx.x; q < elems; q += blockDim.x)
+      if (Elem<DT>::key(slice_elem<DT>(buf, q)) == wkey && (uint32_t)q < qmin) qmin = (uint32_t)q;
+  }
+  qmin = __reduce_min_sync(0xFFFFFFFFu, qmin);
+  if (lane_id() == 0)
+    wr.top[warp_id()] = qmin == 0xFFFFFFFFu ? 0ull : ((unsigned long long)wkey << 32) | (uint32_t)(0x7FFFFFFF - (int)qmin);
+}
+
+// Row with 1 <= top_k <= kFastK: this warp publishes every element of its vectors at or above
+// a warp-local threshold bin into its own segment of the slice record.  The bin is estimated
+// so that about 2 m elements of the slice pass, m = K/S + 6 sqrt(K/S) + 8: each lane takes the
+// maximum of a few of its elements and the bin is read off the distribution of those maxima
+// (the chance that a lane's e elements contain one of the top fraction f is 1 - (1 - f)^e).
+// A poor estimate costs time, never correctness: the merge checks that enough candidates lie
+// above the highest threshold used.  `hits` is this warp's scratch list (kWarpHits entries).
+template <int DT>
+__device__ __forceinline__ void reduce_slice_fast(const Geometry& g, int sl, int K, const unsigned char* buf, int elems,
+                                                  uint64_t* out_segment, unsigned short* hits, WarpResults& wr) {
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int lane = lane_id(), w = warp_id();
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  const float share = (float)K / (float)g.S;
+  const float m = share + 6.f * sqrtf(share) + 8.f;
+  const float frac = fminf(1.f, 2.f * m / (float)(elems > 0 ? elems : 1));  // fraction of the slice that should pass
+  const int nvec = elems / VEC;
+  const int vec_per_thread = (nvec + (int)blockDim.x - 1) / (int)blockDim.x;
+  int vecs = (int)(0.7f / (frac * VEC) + 0.5f);   // keep frac * (elements looked at) around 0.7 or below
+  vecs = vecs < 1 ? 1 : (vecs > vec_per_thread ? vec_per_thread : vecs);
+  const float p_lane = 1.f - __expf((float)(vecs * VEC) * __logf(fmaxf(1.f - frac, 1e-6f)));
+
+  const uint32_t tkey = thread_max_key<DT>(buf, nvec, vecs);
+  const bool has = (int)threadIdx.x < nvec;
+  const int my_bin = has ? (int)(tkey >> kHistShift) : -1;
+  const int holders = __popc(__ballot_sync(0xFFFFFFFFu, has));
+  int want = (int)((float)holders * p_lane + 0.999f);
+  want = want < 1 ? 1 : want;
+  int bin = 0;   // largest bin such that at least `want` lanes have a maximum at or above it
+#pragma unroll
+  for (int bit = 11; bit >= 0; --bit) {
+    const int mid = bin | (1 << bit);
+    if (__popc(__ballot_sync(0xFFFFFFFFu, my_bin >= mid)) >= want) bin = mid;
+  }
+  // One threshold for the whole slice: the lower quartile of the warps' estimates (a single
+  // warp's estimate is noisy, and the merge can only use the highest threshold of a row).
+  if (lane == 0) wr.bin[w] = holders ? (unsigned short)bin : (unsigned short)0xFFFF;
+  __syncthreads();
+  {
+    const int nw = (int)blockDim.x >> 5;
+    const int j = lane % nw;
+    const uint32_t mine = wr.bin[j];
+    int rank = 0, live = 0;
+    for (int t = 0; t < nw; ++t) {
+      const uint32_t other = wr.bin[t];
+      live += other != 0xFFFFu;
+      rank += (other < mine || (other == mine && t < j)) ? 1 : 0;
+    }
+    const uint32_t pick = __ballot_sync(0xFFFFFFFFu, lane < nw && rank == live / 4);
+    bin = pick ? (int)__shfl_sync(0xFFFFFFFFu, mine, __ffs(pick) - 1) : 0;
+    if (bin == 0xFFFF) bin = 0;
+  }
+  const uint32_t min_key = (uint32_t)bin << kHistShift;
+
+  // step 1: which of this warp's vectors hold an element at or above the threshold
+  int nhits = 0;
+  const uint4* vp = reinterpret_cast<const uint4*>(buf);
+  const float thr = bin_lower_value(bin);
+  const __nv_bfloat162 thr2 = __float2bfloat162_rn(thr);   // bin edges are exact in bf16
+  for (int i0 = w * 32; i0 < nvec; i0 += blockDim.x) {
+    const int i = i0 + lane;
+    bool hit = false;
+    if (i < nvec) {
+      const uint4 v = vp[i];
+      if constexpr (DT == TLX_BF16) {
+        // __hblt2: both halves ordered and below the threshold (a NaN fails it and is looked at)
+        hit = !(__hblt2(bf162_bits(v.x), thr2) && __hblt2(bf162_bits(v.y), thr2) && __hblt2(bf162_bits(v.z), thr2) &&
+                __hblt2(bf162_bits(v.w), thr2));
+      } else {
+        hit = !(__uint_as_float(v.x) < thr && __uint_as_float(v.y) < thr && __uint_as_float(v.z) < thr &&
+                __uint_as_float(v.w) < thr);
+      }
+    }
+    const uint32_t mask = __ballot_sync(0xFFFFFFFFu, hit);
+    if (hit) hits[nhits + __popc(mask & lt_mask)] = (unsigned short)i;
+    nhits += __popc(mask);
+  }
+  __syncwarp();
+  // step 2: expand the noted vectors densely and publish what passes
+  int count = 0;
+  auto offer = [&](bool valid, int q) {
+    uint32_t key = 0;
+    bool pass = false;
+    if (valid) {
+      key = Elem<DT>::key(slice_elem<DT>(buf, q));
+      pass = key >= min_key;
+    }
+    const uint32_t mask = __ballot_sync(0xFFFFFFFFu, pass);
+    if (pass) {
+      const int pos = count + __popc(mask & lt_mask);
+      if (pos < kWarpCap) out_segment[pos] = cand_make(key, (uint32_t)g.column(sl, q));
+    }
+    count += __popc(mask);
+  };
+  for (int e0 = 0; e0 < nhits * VEC; e0 += 32) {
+    const int e = e0 + lane;
+    const bool valid = e < nhits * VEC;
+    offer(valid, valid ? (int)hits[e / VEC] * VEC + (e % VEC) : 0);
+  }
+  if (w == 0)   // ragged tail of the row's last slice (fewer than VEC elements)
+    for (int q0 = nvec * VEC; q0 < elems; q0 += 32) offer(q0 + lane < elems, q0 + lane);
+  if (lane == 0) {
+    wr.count[w] = (unsigned short)(count < kWarpCap ? count : kWarpCap);
+    wr.overflow[w] = count > kWarpCap ? 1 : 0;
+    if (w == 0) wr.cutoff_bin = bin;
+  }
+}
+
+// bf16 row without a small top-k: slice maximum, full-key histogram of the kWin keys below
+// it (published as 16-bit counts: a slice holds fewer than 65536 elements), and the sum of
+// exp(x - slice max).  `win` is the CTA's kWin-bin area.
+__device__ __forceinline__ void reduce_slice_general_bf16(const SampleParams& p, const Geometry& g, int64_t row,
+                                                          int sl, const unsigned char* buf, int elems,
+                                                          SelectShared& s, uint32_t* win) {
+  using T = __nv_bfloat16;
+  SliceHeader* hdr = record_header(p, row, sl);
+  uint32_t* out = reinterpret_cast<uint32_t*>(record_payload(p, row, sl));
   uint64_t best = 0;
-  for_each_elem<DT>(row, 0, n, [&](T v, int64_t c) {
-    uint64_t x = ((uint64_t)Elem<DT>::key(v) << 32) | (uint32_t)(0x7FFFFFFF - (int32_t)c);
+  for_each_slice_elem<TLX_BF16>(buf, elems, [&](T v, int) {
+    const uint64_t x = (uint64_t)Elem<TLX_BF16>::key(v);
     best = x > best ? x : best;
   });
   block_max_u64(best, s);
-  return best;
-}
-
-__device__ __forceinline__ void worklist_push(int32_t* wl, int32_t row) {
-  const int slot = atomicAdd(wl, 1);
-  wl[1 + slot] = row;
-}
-
-// ---------------------------------------------------------------------------------
-// fast kernel
-// ---------------------------------------------------------------------------------
-template <int DT>
-__global__ void __launch_bounds__(kFastThreads) sample_fast_kernel(SampleParams p) {
-  using T = typename Elem<DT>::type;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
-  uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
-  const int64_t r = blockIdx.x;
-  const T* row = reinterpret_cast<const T*>(p.logits) + r * p.row_stride;
-  int K = p.top_k[r];
-  if (K <= 0 || (int64_t)K >= p.vocab) K = (int)p.vocab;
-  const float T_ = p.temperature[r];
-  const float pp = p.top_p[r];
-
-  if (T_ < kSamplingEps) {
-    const uint64_t best = row_argmax<DT>(row, p.vocab, s);
-    if (threadIdx.x == 0) {
-      p.out_tokens[r] = 0x7FFFFFFF - (int32_t)(uint32_t)best;
-      if (p.out_status) p.out_status[r] = 0;
-    }
-    return;
-  }
-  if (K > kFastK) {
-    if (threadIdx.x == 0) worklist_push(p.worklist, (int32_t)r);
-    return;
-  }
-  if (!collect_row<DT, kFastCap>(row, p.vocab, K, s, cand)) {
-    if (threadIdx.x == 0) worklist_push(p.worklist, (int32_t)r);
-    return;
-  }
-  const int m = s.fill;
-  sort_candidates(cand, m);
-  const int64_t nrow = r + p.dim0_offset;
-  const int tok = sample_tail<2>(
-      K, pp, T_, s, [&](int i) { return key_f32(cand_key(cand[i])); },
-      [&](int i) { return (int)cand_low(cand[i]); },
-      [&](int i) { return p.noise.at(nrow, (int64_t)cand_low(cand[i])); });
-  if (threadIdx.x == 0) {
-    p.out_tokens[r] = tok;
-    if (p.out_status) p.out_status[r] = 0;
-  }
-}
-
-// ---------------------------------------------------------------------------------
-// general path pieces
-// ---------------------------------------------------------------------------------
-// Softmax denominator over the top-k set by streaming: sum of exp(x - xmax) over keys
-// > vk (all keys when !bounded); the caller adds the admitted ties.
-template <int DT>
-__device__ __forceinline__ double stream_mass(const typename Elem<DT>::type* __restrict__ row, int64_t n, float xmax,
-                                              bool bounded, uint32_t vk, SelectShared& s) {
-  using T = typename Elem<DT>::type;
-  // compensated f32 sum per thread (the exp itself is f32), f64 across threads
-  float sum = 0.f, comp = 0.f;
-  for_each_elem<DT>(row, 0, n, [&](T v, int64_t) {
-    const uint32_t key = Elem<DT>::key(v);
-    if (!bounded || key > vk) {
-      const float y = expf(elem_as_float<DT>(v) - xmax) - comp;
-      const float t = sum + y;
-      comp = (t - sum) - y;
-      sum = t;
-    }
+  const uint32_t kmax32 = (uint32_t)best;
+  const int kmax = (int)(kmax32 >> 16);
+  const float smax = key_f32(kmax32);
+  for (int i = threadIdx.x; i < kWin; i += blockDim.x) win[i] = 0;
+  __syncthreads();
+  float part = 0.f;
+  for_each_slice_elem<TLX_BF16>(buf, elems, [&](T v, int) {
+    const int d = kmax - (int)(Elem<TLX_BF16>::key(v) >> 16);
+    if (d < kWin) atomicAdd(&win[d], 1u);
+    part += expf(__bfloat162float(v) - smax);
   });
-  const double acc = (double)sum - (double)comp;
   double total;
-  block_scan_incl<double>(acc, s.scan_f64, &total, ShflUpF64());
-  return total;
-}
-
-// Streaming Gumbel arg-max over the kept elements:
-//   key >= vstar, and inside the top-k set: key > vk, or key == vk with tie rank < ties_admitted
-// (rank = number of equal keys at lower columns).  `ordered` selects the traversal that
-// tracks tie ranks; it is only needed when the kept set cuts through the tie group.
-//
-// The score y = x / T + gumbel(u) is screened in f32: every thread keeps its two best
-// screened scores, the block maximum A is reduced, and only elements within kGumbelSlack
-// of A are decided on the f64-evaluated Gumbel term.  If some thread has two elements that
-// close to A (there may then be a third), the row is traversed once more instead.
-template <int DT, typename F>
-__device__ __forceinline__ void for_each_kept(const typename Elem<DT>::type* __restrict__ row, int64_t n,
-                                              uint32_t vstar, bool bounded, uint32_t vk, uint32_t ties_admitted,
-                                              bool ordered, SelectShared& s, F&& f) {
-  using T = typename Elem<DT>::type;
-  if (!ordered) {
-    for_each_elem<DT>(row, 0, n, [&](T v, int64_t c) {
-      const uint32_t key = Elem<DT>::key(v);
-      if (key >= vstar && (!bounded || key >= vk)) f(elem_as_float<DT>(v), c);
-    });
-  } else {
-    const int64_t L = (n + blockDim.x - 1) / blockDim.x;
-    const int64_t b0 = (int64_t)threadIdx.x * L, b1 = (b0 + L < n) ? b0 + L : n;
-    uint32_t ties = 0;
-    for (int64_t c = b0; c < b1; ++c) ties += (Elem<DT>::key(row[c]) == vk);
-    uint32_t tot;
-    uint32_t rank = block_scan_incl<uint32_t>(ties, s.scan_u32, &tot, ShflUpU32()) - ties;
-    for (int64_t c = b0; c < b1; ++c) {
-      const T v = row[c];
-      const uint32_t key = Elem<DT>::key(v);
-      if (key > vk) { if (key >= vstar) f(elem_as_float<DT>(v), c); }
-      else if (key == vk) { if (rank < ties_admitted && key >= vstar) f(elem_as_float<DT>(v), c); rank++; }
-    }
+  block_scan_incl<double>((double)part, s.scan_f64, &total, ShflUpF64());
+  for (int i = threadIdx.x; i < kWin / 2; i += blockDim.x) out[i] = win[2 * i] | (win[2 * i + 1] << 16);
+  if (threadIdx.x == 0) {
+    hdr->kmax16 = kmax;
+    hdr->smax = smax;
+    hdr->mass = total;
+    hdr->top = ((unsigned long long)kmax32 << 32) | 1ull;
   }
 }
 
-__device__ __forceinline__ Best block_best(Best best, SelectShared& s) {
-  best = warp_best(best);
-  __syncthreads();
-  if (lane_id() == 0) { s.scan_f64[warp_id()] = (double)best.y; s.scan_u32[warp_id()] = (uint32_t)best.tok; }
-  __syncthreads();
-  const int nw = (blockDim.x + 31) >> 5;
-  Best b{-INFINITY, 0x7FFFFFFF};
-  for (int w = 0; w < nw; ++w) b = best_of(b, Best{(float)s.scan_f64[w], (int)s.scan_u32[w]});
-  __syncthreads();
-  return b;
+// ---- row merges (run by the CTA that completed the row's last slice) ------------------------
+template <typename T>
+__device__ __forceinline__ T ld_cg(const T* p) { return __ldcg(p); }
+
+__device__ __forceinline__ int merge_row_greedy(const SampleParams& p, int64_t row, SelectShared& s) {
+  uint64_t best = 0;
+  if ((int)threadIdx.x < p.S) best = ld_cg(&record_header(p, row, threadIdx.x)->top);
+  block_max_u64(best, s);
+  return 0x7FFFFFFF - (int32_t)(uint32_t)best;
 }
 
-template <int DT>
-__device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n, float T_,
-                                            uint32_t vstar, bool bounded, uint32_t vk, uint32_t ties_admitted,
-                                            bool ordered, const NoiseSrc& noise, int64_t nrow, SelectShared& s) {
-  // screening pass: two best screened scores per thread, with what is needed to re-evaluate the best
+// Gathers the published candidates of a row that lie at or above the highest slice threshold
+// into cand[]; returns their number, or -1 if the published sets cannot be trusted to hold
+// the row's top-K (a segment overflowed, or fewer than K candidates).  A row's candidates
+// sit in S * kWarps segments (one per slice and publishing warp).
+__device__ __forceinline__ int gather_candidates(const SampleParams& p, int64_t row, int K, SelectShared& s,
+                                                 uint64_t* cand) {
+  if (threadIdx.x == 0) { s.tmp_i[0] = 0; s.tmp_i[1] = 0; s.fill = 0; }
+  __syncthreads();
+  const int nseg = p.S * kWarps;
+  uint32_t carry = 0;
+  for (int base = 0; base < nseg; base += blockDim.x) {
+    const int seg = base + threadIdx.x;
+    uint32_t cnt = 0;
+    if (seg < nseg) {
+      const SliceHeader* h = record_header(p, row, seg / kWarps);
+      cnt = ld_cg(&h->wcount[seg % kWarps]);
+      if (seg % kWarps == 0) {
+        atomicMax(&s.tmp_i[0], ld_cg(&h->cutoff_bin));
+        if (ld_cg(&h->overflow)) atomicOr(&s.tmp_i[1], 1);
+      }
+    }
+    uint32_t total;
+    const uint32_t incl = block_scan_incl<uint32_t>(cnt, s.scan_u32, &total, ShflUpU32());
+    if (seg < nseg) s.hist[seg] = carry + incl;   // inclusive offsets of the segments
+    carry += total;
+  }
+  __syncthreads();
+  if (s.tmp_i[1] != 0) return -1;
+  const uint32_t min_key = (uint32_t)s.tmp_i[0] << kHistShift;
+  for (uint32_t f = threadIdx.x; f < carry; f += blockDim.x) {
+    int lo = 0, hi = nseg - 1;   // first segment whose inclusive offset exceeds f
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (s.hist[mid] > f) hi = mid; else lo = mid + 1;
+    }
+    const uint32_t before = lo ? s.hist[lo - 1] : 0u;
+    const uint64_t* seg_base =
+        reinterpret_cast<const uint64_t*>(record_payload(p, row, lo / kWarps)) + (lo % kWarps) * kWarpCap;
+    const uint64_t c = ld_cg(seg_base + (f - before));
+    if (cand_key(c) >= min_key) {
+      const int slot = atomicAdd(&s.fill, 1);
+      if (slot < kMergeCap) cand[slot] = c;
+    }
+  }
+  __syncthreads();
+  const int m = s.fill;
+  return (m > kMergeCap || m < K) ? -1 : m;
+}
+
+// Sampler tail on unsorted bf16 candidates, without sorting them: a histogram over the
+// candidates' 16-bit keys gives the top-k boundary (key and admitted ties), the softmax
+// denominator and the top-p threshold exactly as in the whole-row path (the mass of a value
+// group is count * exp(value - max)); the Gumbel arg-max then runs over the kept candidates.
+// Needs the keys to span at most kHistBins values; returns -1 otherwise (caller sorts).
+__device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row, int K, float pp, float T_, int m,
+                                              SelectShared& s, const uint64_t* cand) {
+  uint32_t kmx = 0, kmn = 0xFFFFFFFFu;
+  for (int i = threadIdx.x; i < m; i += blockDim.x) {
+    const uint32_t k16 = cand_key(cand[i]) >> 16;
+    kmx = k16 > kmx ? k16 : kmx;
+    kmn = k16 < kmn ? k16 : kmn;
+  }
+  const int kmax = (int)block_max_u32(kmx, s.scan_u32);
+  const int kmin = (int)block_min_u32(kmn, s.scan_u32);
+  const int W = kmax - kmin + 1;
+  if (W > kHistBins) return -1;
+  uint32_t* win = s.hist;   // win[kmax - key16]
+  for (int i = threadIdx.x; i < W; i += blockDim.x) win[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < m; i += blockDim.x) atomicAdd(&win[kmax - (int)(cand_key(cand[i]) >> 16)], 1u);
+  __syncthreads();
+  const float xmax = key16_value(kmax);
+  const int per = (W + (int)blockDim.x - 1) / (int)blockDim.x;
+  const int i0 = threadIdx.x * per;
+
+  // top-k boundary: first bin (descending key) at which the running count reaches K
+  uint32_t local = 0;
+  for (int j = 0; j < per; ++j) if (i0 + j < W) local += win[i0 + j];
+  uint32_t total;
+  const uint32_t incl = block_scan_incl<uint32_t>(local, s.scan_u32, &total, ShflUpU32());
+  const uint32_t before = incl - local;
+  if (before < (uint32_t)K && incl >= (uint32_t)K) {
+    uint32_t run = before;
+    for (int j = 0; j < per; ++j) {
+      const uint32_t c = win[i0 + j];
+      if (run + c >= (uint32_t)K) { s.tmp_i[0] = i0 + j; s.tmp_i[1] = (int)((uint32_t)K - run); s.tmp_i[2] = (int)c; break; }
+      run += c;
+    }
+  }
+  __syncthreads();
+  const int vk_idx = s.tmp_i[0];
+  const uint32_t ties_admitted = (uint32_t)s.tmp_i[1], ties_total = (uint32_t)s.tmp_i[2];
+
+  // denominator and top-p threshold over the top-k set
+  double mass = 0.0;
+  for (int j = 0; j < per; ++j) {
+    const int idx = i0 + j;
+    if (idx < W && idx <= vk_idx) {
+      const uint32_t c = idx == vk_idx ? ties_admitted : win[idx];
+      if (c) mass += (double)c * (double)expf(key16_value(kmax - idx) - xmax);
+    }
+  }
+  double Z;
+  const double mincl = block_scan_incl<double>(mass, s.scan_f64, &Z, ShflUpF64());
+  const double target = (double)pp * Z;
+  if (threadIdx.x == 0) s.tmp_i[3] = vk_idx;   // default: keep the whole top-k set
+  __syncthreads();
+  if (mincl - mass < target && mincl >= target) {
+    double run = mincl - mass;
+    for (int j = 0; j < per; ++j) {
+      const int idx = i0 + j;
+      if (idx < W && idx <= vk_idx) {
+        const uint32_t c = idx == vk_idx ? ties_admitted : win[idx];
+        if (c) {
+          run += (double)c * (double)expf(key16_value(kmax - idx) - xmax);
+          if (run >= target) { s.tmp_i[3] = idx; break; }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int vstar_idx = s.tmp_i[3];
+  const bool cut_ties = vstar_idx == vk_idx && ties_admitted < ties_total;
+  __syncthreads();
+
+  // the lowest tokens of the boundary group are the admitted ones: list the group's tokens
+  uint32_t* tie_tok = s.hist;   // the histogram is no longer needed
+  if (cut_ties) {
+    if (threadIdx.x == 0) s.fill = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < m; i += blockDim.x) {
+      const uint64_t c = cand[i];
+      if (kmax - (int)(cand_key(c) >> 16) == vk_idx) tie_tok[atomicAdd(&s.fill, 1)] = cand_low(c);
+    }
+    __syncthreads();
+  }
+  const int n_ties = cut_ties ? s.fill : 0;
+
+  // Gumbel arg-max over the kept candidates, screened in f32 (see final_argmax)
+  const int64_t nrow = row + p.dim0_offset;
   float a1 = -INFINITY, a2 = -INFINITY, q1 = 0.f, u1 = 0.5f;
   int c1 = 0x7FFFFFFF;
-  for_each_kept<DT>(row, n, vstar, bounded, vk, ties_admitted, ordered, s, [&](float x, int64_t c) {
-    const float u = noise.at(nrow, c);
-    const float q = __fdiv_rn(x, T_);
-    const float a = q + gumbel_fast(u);
-    if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = u; c1 = (int)c; }
-    else if (a > a2) a2 = a;
-  });
+  auto kept = [&](uint64_t c) {
+    const int idx = kmax - (int)(cand_key(c) >> 16);
+    if (idx > vstar_idx) return false;
+    if (idx < vk_idx || !cut_ties) return true;
+    uint32_t rank = 0;   // idx == vk_idx: admitted if fewer than ties_admitted group members have a lower token
+    const uint32_t tok = cand_low(c);
+    for (int j = 0; j < n_ties; ++j) rank += tie_tok[j] < tok ? 1u : 0u;
+    return rank < ties_admitted;
+  };
+  for (int i = threadIdx.x; i < m; i += blockDim.x) {
+    const uint64_t c = cand[i];
+    if (kept(c)) {
+      const float u = p.noise.at(nrow, (int64_t)cand_low(c));
+      const float q = __fdiv_rn(key_f32(cand_key(c)), T_);
+      const float a = q + gumbel_fast(u);
+      if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = u; c1 = (int)cand_low(c); }
+      else if (a > a2) a2 = a;
+    }
+  }
   const Best top = block_best(Best{a1, c1}, s);
   const float cut = top.y - (kGumbelSlack + 1e-5f * fabsf(top.y));
   const int crowded = __syncthreads_or(a2 >= cut);
@@ -214,266 +653,247 @@ __device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __res
   if (!crowded) {
     if (a1 >= cut) best = Best{q1 + gumbel_exact(u1), c1};
   } else {
-    for_each_kept<DT>(row, n, vstar, bounded, vk, ties_admitted, ordered, s, [&](float x, int64_t c) {
-      const float u = noise.at(nrow, c);
-      const float q = __fdiv_rn(x, T_);
-      if (q + gumbel_fast(u) >= cut) best = best_of(best, Best{q + gumbel_exact(u), (int)c});
-    });
+    for (int i = threadIdx.x; i < m; i += blockDim.x) {
+      const uint64_t c = cand[i];
+      if (kept(c)) {
+        const float u = p.noise.at(nrow, (int64_t)cand_low(c));
+        const float q = __fdiv_rn(key_f32(cand_key(c)), T_);
+        if (q + gumbel_fast(u) >= cut) best = best_of(best, Best{q + gumbel_exact(u), (int)cand_low(c)});
+      }
+    }
   }
   return block_best(best, s).tok;
 }
 
-// ---- bf16: 16-bit keys ---------------------------------------------------------------
-__device__ __forceinline__ uint32_t key16_to_key32(uint32_t k16) {
-  return (k16 << 16) | ((k16 & 0x8000u) ? 0u : 0xFFFFu);
-}
-
-// Histogram of the keys in [whi - kWindow + 1, whi] into win[whi - key16].
-__device__ __forceinline__ void window_hist(const __nv_bfloat16* __restrict__ row, int64_t n, int whi, uint32_t* win) {
-  for (int i = threadIdx.x; i < kWindow; i += blockDim.x) win[i] = 0;
+template <int DT>
+__device__ __forceinline__ int merge_row_fast(const SampleParams& p, int64_t row, int K, float pp, float T_,
+                                              SelectShared& s, uint64_t* cand, int* status) {
+  using T = typename Elem<DT>::type;
+  const T* rowp = reinterpret_cast<const T*>(p.logits) + row * p.row_stride;
+  int m = gather_candidates(p, row, K, s, cand);
   __syncthreads();
-  for_each_elem<TLX_BF16>(row, 0, n, [&](__nv_bfloat16 v, int64_t) {
-    const int d = whi - (int)(Elem<TLX_BF16>::key(v) >> 16);
-    if (d >= 0 && d < kWindow) atomicAdd(&win[d], 1u);
-  });
-  __syncthreads();
-}
-
-__global__ void __launch_bounds__(kGenThreads) sample_general_bf16_kernel(SampleParams p) {
-  using T = __nv_bfloat16;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
-  uint32_t* win = reinterpret_cast<uint32_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
-  constexpr int kPer = kWindow / kGenThreads;  // window slots per thread, descending key order
-  const int count = p.worklist[0];
-  for (int w = blockIdx.x; w < count; w += gridDim.x) {
-    const int64_t r = p.worklist[1 + w];
-    const T* row = reinterpret_cast<const T*>(p.logits) + r * p.row_stride;
-    const int64_t n = p.vocab;
-    int K = p.top_k[r];
-    if (K <= 0 || (int64_t)K >= n) K = (int)n;
-    const bool bounded = (int64_t)K < n;
-    const float T_ = p.temperature[r];
-    const double target_frac = (double)p.top_p[r];
-
-    const uint64_t top = row_argmax<TLX_BF16>(row, n, s);
-    const int kmax = (int)((uint32_t)(top >> 32) >> 16);
-    const float xmax = key_f32((uint32_t)(top >> 32));
-
-    // ---- phase A: the top-k boundary (key vk, admitted ties) by counts ----------------
-    int vk16 = -1;
-    uint32_t ties_admitted = 0, ties_total = 0;
-    int hist_whi = -1;  // window currently held in `win`
-    if (bounded) {
-      uint32_t cnt_hi = 0;
-      for (int whi = kmax; whi >= 0; whi -= kWindow) {
-        window_hist(row, n, whi, win);
-        hist_whi = whi;
-        uint32_t local = 0;
-        const int i0 = threadIdx.x * kPer;
-        for (int j = 0; j < kPer; ++j) local += win[i0 + j];
-        uint32_t total;
-        const uint32_t incl = block_scan_incl<uint32_t>(local, s.scan_u32, &total, ShflUpU32());
-        const uint32_t before = cnt_hi + incl - local;
-        if (before < (uint32_t)K && before + local >= (uint32_t)K) {
-          uint32_t run = before;
-          for (int j = 0; j < kPer; ++j) {
-            const uint32_t c = win[i0 + j];
-            if (run + c >= (uint32_t)K) {
-              s.tmp_i[0] = whi - (i0 + j);
-              s.tmp_i[1] = (int)((uint32_t)K - run);
-              s.tmp_i[2] = (int)c;
-              break;
-            }
-            run += c;
-          }
-        }
-        __syncthreads();
-        if (cnt_hi + total >= (uint32_t)K) {
-          vk16 = s.tmp_i[0];
-          ties_admitted = (uint32_t)s.tmp_i[1];
-          ties_total = (uint32_t)s.tmp_i[2];
-          __syncthreads();
-          break;
-        }
-        cnt_hi += total;
-        __syncthreads();
-      }
-    }
-    const uint32_t vk32 = vk16 >= 0 ? key16_to_key32((uint32_t)vk16) : 0u;
-
-    // ---- phase B: softmax denominator over the top-k set -------------------------------
-    double Z = stream_mass<TLX_BF16>(row, n, xmax, bounded, vk32, s);
-    if (bounded) Z += (double)ties_admitted * (double)expf(key_f32(vk32) - xmax);
-    const double target = target_frac * Z;
-
-    // ---- phase C: top-p threshold = first value group (descending) whose cumulative mass
-    //      over the top-k set reaches top_p * Z ---------------------------------------------
-    int vstar16 = bounded ? vk16 : 0;
-    {
-      double cum = 0.0;
-      const int lowest = bounded ? vk16 : 0;
-      for (int whi = kmax; whi >= lowest; whi -= kWindow) {
-        if (hist_whi != whi) { window_hist(row, n, whi, win); hist_whi = whi; }
-        const int i0 = threadIdx.x * kPer;
-        double local = 0.0;
-        for (int j = 0; j < kPer; ++j) {
-          const int k16 = whi - (i0 + j);
-          uint32_t c = win[i0 + j];
-          if (bounded) { if (k16 < vk16) c = 0; else if (k16 == vk16) c = ties_admitted; }
-          if (c && k16 >= 0) local += (double)c * (double)expf(key_f32(key16_to_key32((uint32_t)k16)) - xmax);
-        }
-        double total;
-        const double incl = block_scan_incl<double>(local, s.scan_f64, &total, ShflUpF64());
-        const double before = cum + incl - local;
-        if (threadIdx.x == 0) s.tmp_i[3] = -1;
-        __syncthreads();
-        if (before < target && before + local >= target) {
-          double run = before;
-          for (int j = 0; j < kPer; ++j) {
-            const int k16 = whi - (i0 + j);
-            uint32_t c = win[i0 + j];
-            if (bounded) { if (k16 < vk16) c = 0; else if (k16 == vk16) c = ties_admitted; }
-            if (c && k16 >= 0) {
-              run += (double)c * (double)expf(key_f32(key16_to_key32((uint32_t)k16)) - xmax);
-              if (run >= target) { s.tmp_i[3] = k16; break; }
-            }
-          }
-        }
-        __syncthreads();
-        const int found = s.tmp_i[3];
-        __syncthreads();
-        if (found >= 0) { vstar16 = found; break; }
-        cum += total;
-      }
-    }
-    const uint32_t vstar32 = key16_to_key32((uint32_t)vstar16) & (vstar16 == 0 ? 0u : 0xFFFFFFFFu);
-    const bool ordered = bounded && vstar16 == vk16 && ties_admitted < ties_total;
-    const int tok = final_argmax<TLX_BF16>(row, n, T_, vstar32, bounded, vk32, ties_admitted, ordered, p.noise,
-                                           r + p.dim0_offset, s);
-    if (threadIdx.x == 0) {
-      p.out_tokens[r] = tok;
-      if (p.out_status) p.out_status[r] = 1;
-    }
+  if (m < 0) {
+    exact_select_row<DT>(rowp, p.vocab, K, s, cand);
+    m = K;
+    *status |= kStatusRedone;
     __syncthreads();
   }
+  if constexpr (DT == TLX_BF16) {
+    const int tok = tail_bf16_hist(p, row, K, pp, T_, m, s, cand);
+    if (tok >= 0) return tok;
+    __syncthreads();
+  }
+  sort_candidates(cand, m);
+  const int64_t nrow = row + p.dim0_offset;
+  return sample_tail<2>(
+      K, pp, T_, s, [&](int i) { return key_f32(cand_key(cand[i])); }, [&](int i) { return (int)cand_low(cand[i]); },
+      [&](int i) { return p.noise.at(nrow, (int64_t)cand_low(cand[i])); });
 }
 
-// ---- any float dtype: 32-bit keys, radix digits of 12 / 12 / 8 bits -----------------------
+__device__ __forceinline__ int merge_row_general_bf16(const SampleParams& p, int64_t row, int K, float pp, float T_,
+                                                      SelectShared& s, uint32_t* win) {
+  const __nv_bfloat16* rowp = reinterpret_cast<const __nv_bfloat16*>(p.logits) + row * p.row_stride;
+  if (threadIdx.x == 0) s.tmp_i[0] = 0;
+  __syncthreads();
+  float smax = 0.f;
+  double mass = 0.0;
+  if ((int)threadIdx.x < p.S) {
+    const SliceHeader* h = record_header(p, row, threadIdx.x);
+    const int k = ld_cg(&h->kmax16);
+    s.hist[256 + threadIdx.x] = (uint32_t)k;
+    atomicMax(&s.tmp_i[0], k);
+    smax = ld_cg(&h->smax);
+    mass = ld_cg(&h->mass);
+  }
+  __syncthreads();
+  const int kmax = s.tmp_i[0];
+  const float xmax = key16_value(kmax);
+  double term = ((int)threadIdx.x < p.S) ? mass * (double)expf(smax - xmax) : 0.0;
+  double Z;
+  block_scan_incl<double>(term, s.scan_f64, &Z, ShflUpF64());
+  // window anchored at the row maximum = shifted sum of the slices' windows
+  for (int idx = threadIdx.x; idx < kWin; idx += blockDim.x) {
+    uint32_t acc = 0;
+    for (int sl = 0; sl < p.S; ++sl) {
+      const int j = idx - (kmax - (int)s.hist[256 + sl]);
+      if (j >= 0) {
+        const uint32_t w = ld_cg(reinterpret_cast<const uint32_t*>(record_payload(p, row, sl)) + (j >> 1));
+        acc += (j & 1) ? (w >> 16) : (w & 0xFFFFu);
+      }
+    }
+    win[idx] = acc;
+  }
+  __syncthreads();
+  RowPreset pre;
+  pre.top = ((uint64_t)key16_to_key32((uint32_t)kmax) << 32) | 1ull;
+  pre.have_window = true;
+  pre.mass = Z;
+  return general_row_bf16<kWin>(rowp, p.vocab, K, pp, T_, p.noise, row + p.dim0_offset, s, win, pre);
+}
+
+// ---- the kernels --------------------------------------------------------------------------
+constexpr size_t kSharedHeader = (sizeof(SelectShared) + 15) & ~size_t(15);
+constexpr size_t kUnionBytes = 32768;  // kMergeCap u64 == kWin u32 == kHistBins f64
+constexpr size_t kSlicesSmem = kSharedHeader + kUnionBytes + 2 * (size_t)kSliceBytes + sizeof(Control);
+constexpr size_t kMergeSmem = kSharedHeader + kUnionBytes;
+
+// class and effective top-k of a row, from global memory
+__device__ __forceinline__ int classify_row(const SampleParams& p, int64_t row, int& K) {
+  K = p.top_k[row];
+  if (K <= 0 || (int64_t)K >= p.vocab) K = (int)p.vocab;
+  if (p.temperature[row] < kSamplingEps) return (int)kGreedy;
+  return K <= kFastK ? (int)kFast : (int)kGeneral;
+}
+
+// Kernel 1: persistent CTAs stream the slices (statically assigned: CTA c takes the items
+// c, c + grid, ...) and write one record per slice.  Nothing in the per-slice path waits on
+// a global-memory round trip: while the memory system is saturated by the bulk copies such a
+// round trip costs several microseconds, more than a slice's whole share of the time.
 template <int DT>
-__global__ void __launch_bounds__(kGenThreads) sample_general_radix_kernel(SampleParams p) {
-  using T = typename Elem<DT>::type;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(kThreads, 2) sample_slices_kernel(SampleParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
-  double* mass = reinterpret_cast<double*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
-  constexpr int kPer = kHistBins / kGenThreads;
-  const int shifts[3] = {20, 8, 0};
-  const int bits[3] = {12, 12, 8};
-  const int count = p.worklist[0];
-  for (int w = blockIdx.x; w < count; w += gridDim.x) {
-    const int64_t r = p.worklist[1 + w];
-    const T* row = reinterpret_cast<const T*>(p.logits) + r * p.row_stride;
-    const int64_t n = p.vocab;
-    int K = p.top_k[r];
-    if (K <= 0 || (int64_t)K >= n) K = (int)n;
-    const bool bounded = (int64_t)K < n;
-    const float T_ = p.temperature[r];
+  unsigned char* uni = smem_raw + kSharedHeader;
+  unsigned char* slice_base = uni + kUnionBytes;
+  Control& ctl = *reinterpret_cast<Control*>(uni + kUnionBytes + 2 * (size_t)kSliceBytes);
+  uint32_t* win = reinterpret_cast<uint32_t*>(uni);
+  constexpr int kPublisher = kThreads - 1;
 
-    const uint64_t top = row_argmax<DT>(row, n, s);
-    const float xmax = key_f32((uint32_t)(top >> 32));
+  const Geometry g{p.S, p.chunk_elems, p.nchunks, p.vocab, 31 - __clz(p.chunk_elems), p.div_magic};
+  const int total = (int)(p.rows * p.S);
+  const bool planned = p.rows <= kPlanRows;
 
-    // phase A: K-th largest key and the number of admitted ties, by counting passes
-    uint32_t vk = 0, ties_admitted = 0, ties_total = 0;
-    if (bounded) {
-      uint32_t prefix = 0, prefix_mask = 0;
-      int need = K;
-      for (int d = 0; d < 3; ++d) {
-        const int nb = 1 << bits[d], sh = shifts[d];
-        for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) s.hist[i] = 0;
-        __syncthreads();
-        for_each_elem<DT>(row, 0, n, [&](T v, int64_t) {
-          const uint32_t key = Elem<DT>::key(v);
-          if ((key & prefix_mask) == prefix) atomicAdd(&s.hist[(key >> sh) & (nb - 1)], 1u);
-        });
-        __syncthreads();
-        find_threshold_bin(s, need, 0);
-        const int b = s.bin, above = s.above;
-        const uint32_t cb = s.hist[b];
-        __syncthreads();
-        prefix |= (uint32_t)b << sh;
-        prefix_mask |= (uint32_t)(nb - 1) << sh;
-        need -= above;
-        ties_total = cb;
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl.mbar[0], 1);
+    mbar_init(&ctl.mbar[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    ctl.timeout = 0;
+  }
+  // Plan (small batches): rows whose merge is long (top-k disabled or large) come first, the
+  // others follow in reverse order; class and top-k of every row are kept in shared memory.
+  if (planned) {
+    constexpr int kPer = kPlanRows / kThreads;
+    uint32_t flags[kPer], packed = 0;
+#pragma unroll
+    for (int h = 0; h < kPer; ++h) {
+      const int r = threadIdx.x + h * kThreads;
+      flags[h] = 0;
+      if (r < p.rows) {
+        int K;
+        const int cls = classify_row(p, r, K);
+        flags[h] = cls == kGeneral ? 1u : 0x10000u;
+        ctl.kk[r] = cls == kGeneral ? (unsigned short)0xFFFF : cls == kGreedy ? (unsigned short)0xFFFE
+                                                                               : (unsigned short)K;
       }
-      vk = prefix;
-      ties_admitted = (uint32_t)need;
+      packed += flags[h];
     }
-
-    // phase B: softmax denominator over the top-k set
-    double Z = stream_mass<DT>(row, n, xmax, bounded, vk, s);
-    const double wk = bounded ? (double)expf(key_f32(vk) - xmax) : 0.0;
-    if (bounded) Z += (double)ties_admitted * wk;
-    const double target = (double)p.top_p[r] * Z;
-
-    // phase C: radix descent on cumulative mass
-    uint32_t vstar;
-    {
-      uint32_t prefix = 0, prefix_mask = 0;
-      double cum = 0.0;
-      bool fell_through = false;
-      for (int d = 0; d < 3 && !fell_through; ++d) {
-        const int nb = 1 << bits[d], sh = shifts[d];
-        for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) mass[i] = 0.0;
-        __syncthreads();
-        for_each_elem<DT>(row, 0, n, [&](T v, int64_t) {
-          const uint32_t key = Elem<DT>::key(v);
-          if ((key & prefix_mask) == prefix && (!bounded || key > vk))
-            atomicAdd(&mass[(key >> sh) & (nb - 1)], (double)expf(elem_as_float<DT>(v) - xmax));
-        });
-        __syncthreads();
-        if (threadIdx.x == 0 && bounded && (vk & prefix_mask) == prefix)
-          mass[(vk >> sh) & (nb - 1)] += (double)ties_admitted * wk;
-        if (threadIdx.x == 0) s.tmp_i[3] = -1;
-        __syncthreads();
-        // thread t owns bins [hi - kPer + 1, hi] in descending order
-        const int hi = kHistBins - 1 - threadIdx.x * kPer;
-        double local = 0.0;
-        for (int j = 0; j < kPer; ++j) local += mass[hi - j];
-        double total;
-        const double incl = block_scan_incl<double>(local, s.scan_f64, &total, ShflUpF64());
-        const double before = cum + incl - local;
-        if (before < target && before + local >= target) {
-          double run = before;
-          for (int j = 0; j < kPer; ++j) {
-            const double mj = mass[hi - j];
-            if (mj > 0.0 && run + mj >= target) {
-              s.tmp_i[3] = hi - j;
-              s.scan_f64[36] = run;
-              break;
-            }
-            run += mj;
-          }
-        }
-        __syncthreads();
-        const int found = s.tmp_i[3];
-        const double cum_before = s.scan_f64[36];
-        __syncthreads();
-        if (found < 0) { fell_through = true; break; }
-        prefix |= (uint32_t)found << sh;
-        prefix_mask |= (uint32_t)(nb - 1) << sh;
-        cum = cum_before;
+    uint32_t tot;
+    uint32_t excl = block_scan_incl<uint32_t>(packed, s.scan_u32, &tot, ShflUpU32()) - packed;
+#pragma unroll
+    for (int h = 0; h < kPer; ++h) {
+      const int r = threadIdx.x + h * kThreads;
+      if (r < p.rows) {
+        const int pos = (flags[h] & 1u) ? (int)(excl & 0xFFFFu) : (int)p.rows - 1 - (int)(excl >> 16);
+        ctl.order[pos] = (unsigned short)r;
       }
-      // Mass short of the target (top_p ~ 1 and rounding): keep the whole top-k set.
-      vstar = fell_through ? (bounded ? vk : 0u) : prefix;
+      excl += flags[h];
     }
-    const bool ordered = bounded && vstar == vk && ties_admitted < ties_total;
-    const int tok = final_argmax<DT>(row, n, T_, vstar, bounded, vk, ties_admitted, ordered, p.noise,
-                                     r + p.dim0_offset, s);
-    if (threadIdx.x == 0) {
-      p.out_tokens[r] = tok;
-      if (p.out_status) p.out_status[r] = 1;
+  }
+  __syncthreads();
+  auto row_of = [&](int item) -> int64_t {
+    const int rp = g.div_S(item);
+    return planned ? (int64_t)ctl.order[rp] : (int64_t)rp;
+  };
+  auto class_of = [&](int64_t row, int& K) {
+    if (!planned) return classify_row(p, row, K);
+    const unsigned short v = ctl.kk[row];
+    K = v;
+    return v == 0xFFFE ? (int)kGreedy : v == 0xFFFF ? (int)kGeneral : (int)kFast;
+  };
+  auto load = [&](int item, int b) {
+    if (item < total && warp_id() == 0)
+      issue_slice_load<DT>(p, g, row_of(item), item - g.div_S(item) * p.S, slice_base + (size_t)b * kSliceBytes,
+                           &ctl.mbar[b]);
+  };
+
+  const int stride = gridDim.x;
+  int cur = blockIdx.x, nxt = cur + stride;
+  int b = 0;
+  uint32_t phases = 0;   // bit i: parity to wait for on barrier i
+  load(cur, 0);
+  load(nxt, 1);
+  // One block-wide barrier per slice in the common case: warps reduce their share of the slice
+  // on their own, then meet once; after that warp 0 refills the buffer and the last thread
+  // writes the record's header while everybody else already waits for the next slice.
+  while (cur < total) {
+    unsigned char* buf = slice_base + (size_t)b * kSliceBytes;
+    if (!mbar_wait(&ctl.mbar[b], (phases >> b) & 1u)) ctl.timeout = 1;
+    phases ^= 1u << b;
+
+    const int64_t row = row_of(cur);
+    const int sl = cur - g.div_S(cur) * p.S;
+    const int elems = g.slice_elems(sl);
+    int K;
+    const int cls = class_of(row, K);
+    WarpResults& wr = ctl.wr[b];
+    if (cls == kGreedy) {
+      reduce_slice_greedy<DT>(buf, elems, wr);
+    } else if (cls == kFast) {
+      uint64_t* segment = reinterpret_cast<uint64_t*>(record_payload(p, row, sl)) + warp_id() * kWarpCap;
+      reduce_slice_fast<DT>(g, sl, K, buf, elems, segment, reinterpret_cast<unsigned short*>(uni) + warp_id() * kWarpHits,
+                            wr);
+    } else if constexpr (DT == TLX_BF16) {
+      reduce_slice_general_bf16(p, g, row, sl, buf, elems, s, win);
     }
-    __syncthreads();
+    __syncthreads();   // the slice is reduced and its buffer is free
+    load(nxt + stride, b);
+    if (threadIdx.x == kPublisher) {
+      SliceHeader* hdr = record_header(p, row, sl);
+      if (cls == kGreedy) {
+        unsigned long long best = 0;
+        for (int w = 0; w < kWarps; ++w) best = wr.top[w] > best ? wr.top[w] : best;
+        const int q = 0x7FFFFFFF - (int)(uint32_t)best;
+        const int64_t col = elems > 0 ? g.column(sl, q) : 0;
+        hdr->top = (best & 0xFFFFFFFF00000000ull) | (uint32_t)(0x7FFFFFFF - (int32_t)col);
+      } else if (cls == kFast) {
+        int over = 0;
+        for (int w = 0; w < kWarps; ++w) { hdr->wcount[w] = wr.count[w]; over |= wr.overflow[w]; }
+        hdr->cutoff_bin = wr.cutoff_bin;
+        hdr->overflow = over;
+      }
+    }
+    cur = nxt;
+    nxt += stride;
+    b ^= 1;
+  }
+  if (threadIdx.x == 0 && ctl.timeout) atomicOr(&p.counters[1], 1);
+}
+
+// Kernel 2: one CTA per row turns the row's slice records into a token.
+template <int DT>
+__global__ void __launch_bounds__(kRowThreads) sample_merge_kernel(SampleParams p) {
+  using T = typename Elem<DT>::type;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
+  unsigned char* uni = smem_raw + kSharedHeader;
+  uint64_t* cand = reinterpret_cast<uint64_t*>(uni);
+  uint32_t* win = reinterpret_cast<uint32_t*>(uni);
+  double* massbins = reinterpret_cast<double*>(uni);
+  const int64_t row = blockIdx.x;
+  int K;
+  const int cls = classify_row(p, row, K);
+  const float pp = p.top_p[row], T_ = p.temperature[row];
+  int status = cls == kGeneral ? kStatusGeneral : 0;
+  int tok;
+  if (cls == kGreedy) tok = merge_row_greedy(p, row, s);
+  else if (cls == kFast) tok = merge_row_fast<DT>(p, row, K, pp, T_, s, cand, &status);
+  else if constexpr (DT == TLX_BF16) tok = merge_row_general_bf16(p, row, K, pp, T_, s, win);
+  else tok = general_row_radix<DT>(reinterpret_cast<const T*>(p.logits) + row * p.row_stride, p.vocab, K, pp, T_,
+                                   p.noise, row + p.dim0_offset, s, massbins);
+  if (threadIdx.x == 0) {
+    if (p.counters[1]) status |= kStatusTimeout;
+    p.out_tokens[row] = tok;
+    if (p.out_status) p.out_status[row] = status;
   }
 }
 
@@ -521,7 +941,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(
     const float* __restrict__ cand_vals, const int32_t* __restrict__ cand_idx, const float* __restrict__ cand_noise,
     int n_cand, int k_per_block, int64_t block_stride, int64_t row_stride, const int32_t* __restrict__ top_k,
     const float* __restrict__ top_p, const float* __restrict__ temperature, int32_t* __restrict__ out) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
   const int64_t r = blockIdx.x;
@@ -643,7 +1063,30 @@ static int ensure_smem(const void* func, size_t bytes, const char* what) {
   return TLX_OK;
 }
 
-constexpr size_t kSharedHeader = (sizeof(SelectShared) + 15) & ~size_t(15);
+static int device_sm_count() {
+  static int cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+struct SliceLayout {
+  int S, chunk_elems, nchunks;
+};
+static SliceLayout slice_layout(int64_t vocab, int elem_bytes) {
+  SliceLayout l;
+  l.chunk_elems = kChunkBytes / elem_bytes;
+  l.nchunks = (int)((vocab + l.chunk_elems - 1) / l.chunk_elems);
+  l.S = (l.nchunks + kChunksPerSlice - 1) / kChunksPerSlice;
+  return l;
+}
+static size_t counters_bytes(int64_t rows) { return (((size_t)rows + 2) * sizeof(int32_t) + 255) & ~size_t(255); }
 
 }  // namespace tlx
 
@@ -651,7 +1094,11 @@ using namespace tlx;
 
 extern "C" {
 
-size_t tlx_sample_workspace_bytes(int64_t rows, int64_t) { return rows > 0 ? (size_t)(rows + 1) * sizeof(int32_t) : 0; }
+size_t tlx_sample_workspace_bytes(int64_t rows, int64_t vocab) {
+  if (rows <= 0 || vocab <= 0) return 0;
+  const SliceLayout l = slice_layout(vocab, 4);  // the widest supported element
+  return counters_bytes(rows) + (size_t)rows * l.S * kRecordBytes;
+}
 
 int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab, int64_t row_stride,
                const int32_t* top_k, const float* top_p, const float* temperature, const float* noise,
@@ -666,40 +1113,49 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
   if (rows == 0) return TLX_OK;
   TLX_CHECK_ARG(logits && top_k && top_p && temperature && out_tokens, "sample: null pointer");
   TLX_CHECK_ARG(!noise || noise_stride >= vocab, "sample: noise stride smaller than the row");
-  const size_t need = tlx_sample_workspace_bytes(rows, vocab);
+  const int es = dtype_bytes(dtype);
+  const SliceLayout l = slice_layout(vocab, es);
+  if (l.S > kMaxSlices)
+    return set_error(TLX_ERR_UNSUPPORTED, "sample: vocabulary of %lld needs %d slices per row, at most %d supported",
+                     (long long)vocab, l.S, kMaxSlices);
+  TLX_CHECK_ARG(rows * (int64_t)l.S < (1ll << 30), "sample: too many work items");
+  const size_t need = counters_bytes(rows) + (size_t)rows * l.S * kRecordBytes;
   if (!workspace || workspace_bytes < need)
     return set_error(TLX_ERR_WORKSPACE, "sample: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  TLX_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "sample: workspace must be 16-byte aligned");
 
   SampleParams p{};
   p.logits = logits; p.rows = rows; p.vocab = vocab; p.row_stride = row_stride;
   p.top_k = top_k; p.top_p = top_p; p.temperature = temperature;
   p.noise.dense = noise; p.noise.stride = noise_stride; p.noise.k0 = key0; p.noise.k1 = key1; p.noise.vocab = vocab;
   p.dim0_offset = dim0_offset; p.out_tokens = out_tokens; p.out_status = out_status;
-  p.worklist = (int32_t*)workspace;
+  p.S = l.S; p.chunk_elems = l.chunk_elems; p.nchunks = l.nchunks;
+  p.div_magic = ((1ull << 40) + (unsigned long long)l.S - 1) / (unsigned long long)l.S;
+  // bulk copies need 16-byte aligned row starts and a row length that is a multiple of 16 bytes
+  p.use_tma = ((reinterpret_cast<uintptr_t>(logits) & 15) == 0 && ((row_stride * es) & 15) == 0 && ((vocab * es) & 15) == 0) ? 1 : 0;
+  p.counters = (int32_t*)workspace;
+  p.records = (unsigned char*)workspace + counters_bytes(rows);
 
-  cudaError_t e = cudaMemsetAsync(workspace, 0, sizeof(int32_t), st);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, counters_bytes(rows), st);
   if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaMemsetAsync: %s", cudaGetErrorString(e));
-
-  const size_t fast_smem = kSharedHeader + (size_t)kFastCap * 8;
-  const int gen_blocks = (int)(rows < 148 ? rows : 148);
+  const int64_t items = rows * l.S;
+  const int64_t slots = 2ll * device_sm_count();
+  const unsigned grid = (unsigned)(items < slots ? items : slots);
   int rc;
   if (dtype == TLX_BF16) {
-    const size_t gen_smem = kSharedHeader + (size_t)kWindow * 4;
-    if ((rc = ensure_smem((const void*)sample_fast_kernel<TLX_BF16>, fast_smem, "sample")) != TLX_OK) return rc;
-    if ((rc = ensure_smem((const void*)sample_general_bf16_kernel, gen_smem, "sample")) != TLX_OK) return rc;
-    sample_fast_kernel<TLX_BF16><<<(unsigned)rows, kFastThreads, fast_smem, st>>>(p);
-    TLX_CHECK_LAUNCH("sample (fast kernel)");
-    sample_general_bf16_kernel<<<gen_blocks, kGenThreads, gen_smem, st>>>(p);
-    TLX_CHECK_LAUNCH("sample (general kernel)");
+    if ((rc = ensure_smem((const void*)sample_slices_kernel<TLX_BF16>, kSlicesSmem, "sample")) != TLX_OK) return rc;
+    if ((rc = ensure_smem((const void*)sample_merge_kernel<TLX_BF16>, kMergeSmem, "sample")) != TLX_OK) return rc;
+    sample_slices_kernel<TLX_BF16><<<grid, kThreads, kSlicesSmem, st>>>(p);
+    TLX_CHECK_LAUNCH("sample (slices)");
+    sample_merge_kernel<TLX_BF16><<<(unsigned)rows, kRowThreads, kMergeSmem, st>>>(p);
   } else {
-    const size_t gen_smem = kSharedHeader + (size_t)kHistBins * 8;
-    if ((rc = ensure_smem((const void*)sample_fast_kernel<TLX_F32>, fast_smem, "sample")) != TLX_OK) return rc;
-    if ((rc = ensure_smem((const void*)sample_general_radix_kernel<TLX_F32>, gen_smem, "sample")) != TLX_OK) return rc;
-    sample_fast_kernel<TLX_F32><<<(unsigned)rows, kFastThreads, fast_smem, st>>>(p);
-    TLX_CHECK_LAUNCH("sample (fast kernel)");
-    sample_general_radix_kernel<TLX_F32><<<gen_blocks, kGenThreads, gen_smem, st>>>(p);
-    TLX_CHECK_LAUNCH("sample (general kernel)");
+    if ((rc = ensure_smem((const void*)sample_slices_kernel<TLX_F32>, kSlicesSmem, "sample")) != TLX_OK) return rc;
+    if ((rc = ensure_smem((const void*)sample_merge_kernel<TLX_F32>, kMergeSmem, "sample")) != TLX_OK) return rc;
+    sample_slices_kernel<TLX_F32><<<grid, kThreads, kSlicesSmem, st>>>(p);
+    TLX_CHECK_LAUNCH("sample (slices)");
+    sample_merge_kernel<TLX_F32><<<(unsigned)rows, kRowThreads, kMergeSmem, st>>>(p);
   }
+  TLX_CHECK_LAUNCH("sample");
   return TLX_OK;
 }
 

@@ -41,7 +41,7 @@ __device__ __forceinline__ typename Elem<DT>::type cast_replace(double v) {
 template <int DT, int CAP>
 __global__ void __launch_bounds__(kTopkThreads) topk_kernel(TopkParams p) {
   using T = typename Elem<DT>::type;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
   const int64_t r = blockIdx.x;

@@ -40,7 +40,8 @@ def test_argument_errors_need_no_gpu():
     assert rc == _lib.TLX_ERR_UNSUPPORTED
     assert lib.tlx_sort_workspace_bytes(128, 65536) == 128 * 65536 * 8
     assert lib.tlx_sort_workspace_bytes(16, 2048) == 0
-    assert lib.tlx_sample_workspace_bytes(256, 128256) == 257 * 4
+    assert lib.tlx_sample_workspace_bytes(256, 128256) > 256 * 4
+    assert lib.tlx_sample_workspace_bytes(0, 128256) == 0
 
 
 def test_python_mirror_error_behaviour():

@@ -49,7 +49,8 @@ def test_sample_decode_configuration(cuda, dtype):
     exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
     got, status = _run(cuda, x, tk, tp, T, noise=noise)
     _assert_tokens(got, exp, flags)
-    assert np.array_equal(status != 0, tk == 0)  # only the top-k-disabled rows take the general path
+    assert np.array_equal(status & 1 != 0, tk == 0)  # only the top-k-disabled rows take the general path
+    assert (status & 2 == 0).all()
 
 
 def test_sample_decode_configuration_full_batch(cuda):
@@ -100,7 +101,7 @@ def test_sample_fast_path_overflow_falls_back(cuda):
     exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
     got, status = _run(cuda, x, tk, tp, T, noise=noise)
     _assert_tokens(got, exp, flags, min_checked=0.5)
-    assert (status & 1).all()
+    assert (status & 2 == 0).all()  # no bounded wait gave up
 
 
 def test_sample_with_threefry_key_and_row_offset(cuda):
