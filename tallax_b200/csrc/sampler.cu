@@ -1,26 +1,37 @@
 // Fused temperature / top-k / top-p / noise sampler on [rows, vocab] logits, the
 // candidate-level sampler, and the merge stage of the vocab-sharded sampler.
 //
-// tlx_sample is ONE persistent kernel.  Every row is cut into S slices of interleaved
-// 4 KB chunks; the work items (row, slice) are handed out through an atomic counter and
-// each CTA keeps two slices in shared memory: the one it works on and the next one,
-// which a bulk copy (TMA, cp.async.bulk + mbarrier) is already bringing in.  Logits are
-// therefore read from HBM exactly once, by all SMs at the same rate, whatever the mix
-// of per-row parameters.
+// Every row is seen as S interleaved slices (slice s = the 4 KB chunks s, s + S, ... of the row),
+// each at most 28 KB, so that a slice is a sample of the whole row.  Slices are brought into
+// shared memory with bulk copies (TMA, cp.async.bulk + mbarrier), two buffers per CTA: one is
+// worked on while the next one arrives.  Logits are read from HBM once.
 //
-// A slice is reduced in shared memory to a small record in the workspace:
-//   greedy row (temperature < 1e-5)  : the slice's arg-max;
-//   1 <= top_k <= kFastK             : every element at or above a slice-local threshold
-//                                      bin (chosen from a sample so that about
-//                                      top_k / S + 6 sigma elements pass), plus that bin;
-//   top-k disabled or large, bf16    : slice maximum, histogram over the 8192 16-bit keys
-//                                      below it, and sum of exp(x - slice max).
-// The CTA that completes a row's last slice (atomic count, no waiting) merges the row:
-// candidates at or above the highest slice threshold are a superset of the row's top-k
-// if there are at least top_k of them (checked; otherwise the row is redone exactly from
-// global memory), they are sorted by (value desc, token asc) and the sampler tail runs.
-// Rows without top-k take the top-p threshold from the merged histogram and then stream
-// the row once more (from L2) for the Gumbel arg-max; those rows are scheduled first.
+// tlx_sample, batches with at least one row per two CTA slots (the decode case):
+//   rows kernel    one CTA per row.  Greedy rows keep a running arg-max.  Rows with
+//                  1 <= top_k <= kFastK estimate a threshold bin on their first slice, append
+//                  what lies at or above it to a candidate list in shared memory (one packed
+//                  compare per two elements; the bin is raised exactly, from a histogram of the
+//                  list, when the list fills up) and finish inside the CTA: top-k boundary,
+//                  softmax mass and top-p threshold from a histogram over the candidates' keys
+//                  (bf16; sorted candidates for f32), Gumbel arg-max over the kept ones.
+//   rows whose top-k is disabled (bf16) need per-value counts of the whole row, which only
+//   pays off with every SM helping, so they take three steps:
+//     slices kernel   (before the rows kernel) per slice: maximum, histogram of the 2048 16-bit
+//                     keys below it, sum of exp(x - max) of everything lower;
+//     rows kernel     adds the slices' histograms up, takes the top-p threshold from them (the
+//                     mass of a value group is count * exp(value - max)) and stores it;
+//     slices kernel   (final pass) per slice: Gumbel scores of the elements at or above the
+//                     threshold, the slice's winner goes to the row with an atomic max, the CTA
+//                     that delivers the last slice writes the token.
+//   Rows with a top-k above kFastK, and f32 rows without top-k, are rare enough to take the
+//   multi-pass whole-row routines of sampler_general.cuh.
+// Small batches: all rows are cut into slices (slices kernel, candidates per slice and warp)
+// and merged per row by the merge kernel, so that every SM streams whatever the batch size.
+//
+// Nothing on a per-slice path waits for a global-memory round trip (while the bulk copies
+// saturate the memory system such a round trip costs microseconds), results are exact: a
+// threshold estimate that turns out too high is detected (fewer than top_k candidates) and
+// the row is redone by the exact multi-pass select.
 #include <mutex>
 
 #include "sampler_general.cuh"
@@ -38,10 +49,9 @@ constexpr int kChunkBytes = 4096;    // interleaving granule
 constexpr int kChunksPerSlice = kSliceBytes / kChunkBytes;
 constexpr int kRecordCap = 2048;     // candidates (u64) a slice may publish == 16 KB payload
 constexpr int kMergeCap = 4096;      // candidates (u64) held in shared memory
-constexpr int kWin = 8192;           // bf16 histogram window (bins below the maximum key)
+constexpr int kWin = 2048;           // bf16 histogram window: 16 binades of 16-bit keys below the maximum
 constexpr int kFastK = 1024;         // largest top_k served by the candidate path
 constexpr int kSample = 2048;        // elements of a slice sampled for the first threshold
-constexpr int kPlanRows = 1024;      // rows up to this count are reordered (general rows first)
 constexpr int kMaxSlices = 256;
 constexpr uint32_t kWaitLimit = 1u << 24;  // bounded mbarrier polling
 
@@ -76,6 +86,19 @@ struct WarpResults {
 
 constexpr size_t kRecordBytes = sizeof(SliceHeader) + (size_t)kRecordCap * 8;
 
+constexpr size_t kSharedHeader = (sizeof(SelectShared) + 15) & ~size_t(15);
+constexpr size_t kUnionBytes = 32768;  // kMergeCap candidates (u64) == kHistBins f64 mass bins
+
+// Per row, in the workspace: what the final pass over a row without top-k needs and leaves.
+struct RowState {
+  unsigned int min_key;        // elements with key >= min_key are kept ...
+  float thr;                   // ... and satisfy !(x < thr)
+  unsigned long long best;     // max over slices of key(score) << 32 | (0x7FFFFFFF - token)
+  int done;                    // slices that have delivered their best
+  int pad[3];
+};
+static_assert(sizeof(RowState) == 32, "RowState layout");
+
 struct SampleParams {
   const void* logits;
   int64_t rows, vocab, row_stride;
@@ -91,6 +114,10 @@ struct SampleParams {
   int chunk_elems;     // elements per chunk
   int nchunks;         // chunks per row (the last one may be partial)
   int use_tma;         // row starts and strides are 16-byte aligned
+  int only_general;    // slices kernel: skip rows that the rows kernel finishes on its own
+  int have_records;    // rows kernel: the slices kernel has written the records of the general rows
+  int final_pass;      // slices kernel: score the kept elements of the general rows (third kernel)
+  RowState* rowstate;
   unsigned long long div_magic;  // ceil(2^40 / S)
   // workspace
   int32_t* counters;   // [1] set if a bounded wait gave up
@@ -104,8 +131,10 @@ struct __align__(16) Control {   // per-CTA bookkeeping in shared memory
   int timeout;
   int pad;
   WarpResults wr[2];
-  unsigned short order[kPlanRows];  // planned row order (general rows first)
-  unsigned short kk[kPlanRows];     // per row: top-k (fast rows), 0xFFFE greedy, 0xFFFF general
+  int list_n;                 // slices kernel: this CTA's current batch of items
+  int list[64];
+  uint32_t list_cls[64];
+  unsigned short rows_list[1024];   // slices kernel: the rows it works on, compacted
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -288,6 +317,18 @@ __device__ __forceinline__ typename Elem<DT>::type slice_elem(const unsigned cha
   return reinterpret_cast<const typename Elem<DT>::type*>(buf)[q];
 }
 
+// Threshold bin from one bin per thread: the largest 12-bit bin B such that at least `want`
+// threads have a bin >= B.  One block-wide vote per bit; threads without data vote with -1.
+__device__ __forceinline__ int vote_threshold_bin(int my_bin, int want) {
+  int lo = 0;
+#pragma unroll
+  for (int bit = 11; bit >= 0; --bit) {
+    const int mid = lo | (1 << bit);
+    if (__syncthreads_count(my_bin >= mid) >= want) lo = mid;
+  }
+  return lo;
+}
+
 // Greedy row: this warp's arg-max as key << 32 | (0x7FFFFFFF - local position); positions
 // grow with the column inside a slice, so the lowest position is the lowest column.
 template <int DT>
@@ -437,40 +478,268 @@ __device__ __forceinline__ void reduce_slice_fast(const Geometry& g, int sl, int
   }
 }
 
-// bf16 row without a small top-k: slice maximum, full-key histogram of the kWin keys below
-// it (published as 16-bit counts: a slice holds fewer than 65536 elements), and the sum of
-// exp(x - slice max).  `win` is the CTA's kWin-bin area.
+// bf16 row without a small top-k: slice maximum, full-key histogram of the kWin keys below it
+// (published as 16-bit counts: a slice holds fewer than 65536 elements), and the sum of
+// exp(x - slice max) over the elements BELOW that window.  The softmax mass of a histogram bin
+// is count * exp(value - max), so the merge gets the exact mass of everything in the window
+// from the counts.  `win` is the CTA's kWin-bin area.
 __device__ __forceinline__ void reduce_slice_general_bf16(const SampleParams& p, const Geometry& g, int64_t row,
                                                           int sl, const unsigned char* buf, int elems,
                                                           SelectShared& s, uint32_t* win) {
-  using T = __nv_bfloat16;
   SliceHeader* hdr = record_header(p, row, sl);
   uint32_t* out = reinterpret_cast<uint32_t*>(record_payload(p, row, sl));
-  uint64_t best = 0;
-  for_each_slice_elem<TLX_BF16>(buf, elems, [&](T v, int) {
-    const uint64_t x = (uint64_t)Elem<TLX_BF16>::key(v);
-    best = x > best ? x : best;
-  });
-  block_max_u64(best, s);
-  const uint32_t kmax32 = (uint32_t)best;
+  const int nvec = elems / 8;
+  uint32_t tkey = thread_max_key<TLX_BF16>(buf, nvec, 1 << 30);
+  for (int q = nvec * 8 + threadIdx.x; q < elems; q += blockDim.x) {
+    const uint32_t k = Elem<TLX_BF16>::key(slice_elem<TLX_BF16>(buf, q));
+    tkey = k > tkey ? k : tkey;
+  }
+  const uint32_t kmax32 = block_max_u32(tkey, s.scan_u32);
   const int kmax = (int)(kmax32 >> 16);
   const float smax = key_f32(kmax32);
   for (int i = threadIdx.x; i < kWin; i += blockDim.x) win[i] = 0;
   __syncthreads();
-  float part = 0.f;
-  for_each_slice_elem<TLX_BF16>(buf, elems, [&](T v, int) {
-    const int d = kmax - (int)(Elem<TLX_BF16>::key(v) >> 16);
-    if (d < kWin) atomicAdd(&win[d], 1u);
-    part += expf(__bfloat162float(v) - smax);
-  });
+  // One element = 16 raw bits h.  Its 16-bit key is h + 0x8000 for a cleared sign and 0xFFFF - h
+  // otherwise; its histogram slot is kmax - key if that is inside the window, else exp(x - max)
+  // goes to the below-window sum.  (-0 keeps its own slot next to +0: same value, same mass.)
+  const float neg_smax_l2e = -smax * 1.44269504f;
+  float below = 0.f;
+  auto ex2 = [](float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; };
+  const uint4* vp = reinterpret_cast<const uint4*>(buf);
+  if (kmax >= 0x8000 + kWin) {
+    // positive maximum (the usual case): every negative element is below the window, and one
+    // unsigned compare of (kmax - 0x8000) - h against the window size decides
+    const uint32_t dpos = (uint32_t)(kmax - 0x8000);
+    auto visit = [&](uint32_t h, float x) {
+      const uint32_t d = dpos - h;
+      const float e = ex2(fmaf(x, 1.44269504f, neg_smax_l2e));
+      if (d < (uint32_t)kWin) atomicAdd(&win[d], 1u);
+      else below += e;
+    };
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 v = vp[i];
+      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        visit(w4[j] & 0xFFFFu, __uint_as_float(w4[j] << 16));
+        visit(w4[j] >> 16, __uint_as_float(w4[j] & 0xFFFF0000u));
+      }
+    }
+    for (int q = nvec * 8 + threadIdx.x; q < elems; q += blockDim.x) {
+      const uint32_t h = reinterpret_cast<const unsigned short*>(buf)[q];
+      visit(h, __uint_as_float(h << 16));
+    }
+  } else {
+    auto visit = [&](uint32_t h) {
+      const uint32_t k16 = (h & 0x8000u) ? (~h & 0xFFFFu) : (h | 0x8000u);
+      const int d = kmax - (int)k16;
+      const float e = ex2(fmaf(__uint_as_float(h << 16), 1.44269504f, neg_smax_l2e));
+      if (d >= 0 && d < kWin) atomicAdd(&win[d], 1u);
+      else if (d >= kWin) below += e;
+    };
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 v = vp[i];
+      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { visit(w4[j] & 0xFFFFu); visit(w4[j] >> 16); }
+    }
+    for (int q = nvec * 8 + threadIdx.x; q < elems; q += blockDim.x)
+      visit((uint32_t)reinterpret_cast<const unsigned short*>(buf)[q]);
+  }
   double total;
-  block_scan_incl<double>((double)part, s.scan_f64, &total, ShflUpF64());
+  block_scan_incl<double>((double)below, s.scan_f64, &total, ShflUpF64());
   for (int i = threadIdx.x; i < kWin / 2; i += blockDim.x) out[i] = win[2 * i] | (win[2 * i + 1] << 16);
   if (threadIdx.x == 0) {
     hdr->kmax16 = kmax;
     hdr->smax = smax;
     hdr->mass = total;
     hdr->top = ((unsigned long long)kmax32 << 32) | 1ull;
+  }
+}
+
+// Finds the elements of a tile whose key is >= min_key and hands them to `sink`.  `thr` is a
+// float (exactly representable in the tile's dtype) such that every element with key >= min_key
+// satisfies !(x < thr).  Warp-local in two steps: a packed compare notes the (few) elements that
+// may pass, then those are looked at densely, so that a rare passing element does not drag its
+// whole warp through the slow path.  `hits` is this warp's scratch list of local positions.
+// sink(pass, key, q) is called by all 32 lanes together (pass == false for lanes without one).
+template <int DT, typename Sink>
+__device__ __forceinline__ void scan_tile(const unsigned char* buf, int elems, float thr, uint32_t min_key,
+                                          unsigned short* hits, Sink&& sink) {
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  constexpr int kHitCap = kHistBins * 2 / kWarps;   // the idle histogram holds the warps' lists (u16 entries)
+  const int lane = lane_id(), w = warp_id();
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  const int nvec = elems / VEC;
+  const __nv_bfloat162 thr2 = __float2bfloat162_rn(thr);
+  const uint4* vp = reinterpret_cast<const uint4*>(buf);
+  int nhits = 0;
+  // step 1: per vector, a bit mask of the elements that are not (ordered and) below the threshold
+  auto vec_mask = [&](int i) -> uint32_t {
+    if (i >= nvec) return 0u;
+    const uint4 v = vp[i];
+    if constexpr (DT == TLX_BF16) {
+      const __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(bf162_bits(v.x), bf162_bits(v.y)),
+                                           __hmax2_nan(bf162_bits(v.z), bf162_bits(v.w)));
+      if (__hblt2(m, thr2)) return 0u;   // the common case: nothing in this vector
+      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+      uint32_t bits = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t below = __hlt2_mask(bf162_bits(w4[j]), thr2);   // 0xFFFF per half that is below
+        bits |= ((below & 0xFFFFu) ? 0u : 1u) << (2 * j);
+        bits |= ((below >> 16) ? 0u : 1u) << (2 * j + 1);
+      }
+      return bits;
+    } else {
+      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+      uint32_t bits = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bits |= (__uint_as_float(w4[j]) < thr ? 0u : 1u) << j;
+      return bits;
+    }
+  };
+  // step 2: the noted elements, densely
+  auto offer = [&](bool valid, int q) {
+    uint32_t key = 0;
+    bool pass = false;
+    if (valid) {
+      key = Elem<DT>::key(slice_elem<DT>(buf, q));
+      pass = key >= min_key;
+    }
+    sink(pass, key, q);
+  };
+  auto flush = [&]() {
+    __syncwarp();
+    for (int e0 = 0; e0 < nhits; e0 += 32) offer(e0 + lane < nhits, e0 + lane < nhits ? (int)hits[e0 + lane] : 0);
+    __syncwarp();
+    nhits = 0;
+  };
+  for (int i0 = w * 32; i0 < nvec; i0 += blockDim.x) {
+    const int i = i0 + lane;
+    uint32_t bits = vec_mask(i);
+    while (__any_sync(0xFFFFFFFFu, bits != 0u)) {   // one element per lane and round
+      const bool have = bits != 0u;
+      const uint32_t mask = __ballot_sync(0xFFFFFFFFu, have);
+      if (have) {
+        const int t = __ffs(bits) - 1;
+        bits &= bits - 1;
+        hits[nhits + __popc(mask & lt_mask)] = (unsigned short)(i * VEC + t);
+      }
+      nhits += __popc(mask);
+    }
+    if (nhits > kHitCap - 32 * VEC) flush();   // room for one more round of vectors
+  }
+  flush();
+  if (w == 0)   // ragged tail of the row's last tile (fewer than VEC elements)
+    for (int q0 = nvec * VEC; q0 < elems; q0 += 32) offer(q0 + lane < elems, q0 + lane);
+}
+
+// Appends every element of the tile at or above bin `bin` to the candidate list; `col_of(q)`
+// maps a local position to its column.
+template <int DT, typename ColOf>
+__device__ __forceinline__ void collect_tile(const unsigned char* buf, int elems, int bin, SelectShared& s,
+                                             uint64_t* cand, unsigned short* hits, ColOf col_of) {
+  const uint32_t lt_mask = (1u << lane_id()) - 1u;
+  scan_tile<DT>(buf, elems, bin_lower_value(bin), (uint32_t)bin << kHistShift, hits,
+                [&](bool pass, uint32_t key, int q) {
+                  const uint32_t mask = __ballot_sync(0xFFFFFFFFu, pass);
+                  if (mask) {
+                    int base = 0;
+                    if (lane_id() == __ffs(mask) - 1) base = atomicAdd(&s.fill, __popc(mask));
+                    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(mask) - 1);
+                    if (pass) {
+                      const int pos = base + __popc(mask & lt_mask);
+                      if (pos < kMergeCap) cand[pos] = cand_make(key, (uint32_t)col_of(q));
+                    }
+                  }
+                });
+}
+
+// Raises the threshold bin to the largest one that still has K candidates at or above it and
+// drops the candidates below it.  The histogram is rebuilt from the list (it is not kept up
+// to date while collecting).  All threads call.
+__device__ __forceinline__ void refine_candidates(SelectShared& s, uint64_t* cand, int K) {
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) s.hist[i] = 0;
+  __syncthreads();
+  const int m = s.fill < kMergeCap ? s.fill : kMergeCap;
+  for (int i = threadIdx.x; i < m; i += blockDim.x) atomicAdd(&s.hist[cand_key(cand[i]) >> kHistShift], 1u);
+  const int old_bin = s.bin;
+  __syncthreads();
+  find_threshold_bin(s, K, old_bin);
+  if (s.bin != old_bin) compact_candidates<kMergeCap>(s, cand);
+  __syncthreads();
+}
+
+// Final pass over one slice of a row without top-k: every element with key >= the row's
+// threshold gets its Gumbel score; the slice's winner (decided on the f64-evaluated Gumbel term
+// among the contenders, as in final_argmax) is folded into the row's state with an atomic max,
+// and the CTA that delivers the row's last slice writes the token.
+__device__ __forceinline__ void reduce_slice_final_bf16(const SampleParams& p, const Geometry& g, int64_t row, int sl,
+                                                        const unsigned char* buf, int elems, SelectShared& s,
+                                                        unsigned char* uni) {
+  RowState* rs = p.rowstate + row;
+  const uint32_t min_key = rs->min_key;
+  const float thr = rs->thr;
+  const float T_ = p.temperature[row];
+  const int64_t nrow = row + p.dim0_offset;
+  unsigned short* hits = reinterpret_cast<unsigned short*>(s.hist) + warp_id() * (kHistBins * 2 / kWarps);
+  constexpr int kListCap = (int)(kUnionBytes / 8) / kWarps;
+  constexpr int kListPer = kListCap / 32;
+  uint2* wlist = reinterpret_cast<uint2*>(uni) + warp_id() * kListCap;
+  const uint32_t lt_mask = (1u << lane_id()) - 1u;
+  const float inv_T = 1.0f / T_;
+  float a1 = -INFINITY, a2 = -INFINITY, u1 = 0.5f;
+  uint32_t k1 = 0;
+  int c1 = 0x7FFFFFFF;
+  int wcount = 0;
+  auto score_list = [&](float cut, Best* exact) {
+    __syncwarp();
+    float uu[kListPer];
+#pragma unroll
+    for (int j = 0; j < kListPer; ++j) {
+      const int e = lane_id() + 32 * j;
+      uu[j] = e < wcount ? p.noise.at(nrow, (int64_t)wlist[e].x) : 0.5f;
+    }
+#pragma unroll
+    for (int j = 0; j < kListPer; ++j) {
+      const int e = lane_id() + 32 * j;
+      if (e < wcount) {
+        // screening score: reciprocal instead of the division, fast logs (both well inside the slack)
+        const float a = key_f32(wlist[e].y) * inv_T + gumbel_screen(uu[j]);
+        if (exact) {
+          if (a >= cut)
+            *exact = best_of(*exact, Best{__fdiv_rn(key_f32(wlist[e].y), T_) + gumbel_exact(uu[j]), (int)wlist[e].x});
+        } else if (a > a1) { a2 = a1; a1 = a; k1 = wlist[e].y; u1 = uu[j]; c1 = (int)wlist[e].x; }
+        else if (a > a2) a2 = a;
+      }
+    }
+    __syncwarp();
+    wcount = 0;
+  };
+  auto scan = [&](float cut, Best* exact) {
+    scan_tile<TLX_BF16>(buf, elems, thr, min_key, hits, [&](bool pass, uint32_t key, int q) {
+      const uint32_t mask = __ballot_sync(0xFFFFFFFFu, pass);
+      if (pass) wlist[wcount + __popc(mask & lt_mask)] = make_uint2((uint32_t)g.column(sl, q), key);
+      wcount += __popc(mask);
+      if (wcount > kListCap - 32) score_list(cut, exact);
+    });
+    score_list(cut, exact);
+  };
+  scan(0.f, nullptr);
+  const Best top = block_best(Best{a1, c1}, s);
+  const float cut = top.y - (kGumbelSlack + 1e-5f * fabsf(top.y));
+  Best best{-INFINITY, 0x7FFFFFFF};
+  if (__syncthreads_or(a2 >= cut)) {
+    scan(cut, &best);   // a thread saw two contenders: look at the slice again and decide exactly
+  } else if (a1 >= cut) {
+    best = Best{__fdiv_rn(key_f32(k1), T_) + gumbel_exact(u1), c1};
+  }
+  best = block_best(best, s);
+  if (threadIdx.x == 0 && best.tok != 0x7FFFFFFF) {
+    const unsigned long long packed = ((unsigned long long)f32_key(best.y) << 32) | (uint32_t)(0x7FFFFFFF - best.tok);
+    atomicMax(&rs->best, packed);
   }
 }
 
@@ -541,6 +810,12 @@ __device__ __forceinline__ int gather_candidates(const SampleParams& p, int64_t 
 // Needs the keys to span at most kHistBins values; returns -1 otherwise (caller sorts).
 __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row, int K, float pp, float T_, int m,
                                               SelectShared& s, const uint64_t* cand) {
+#ifdef TLX_PROFILE
+  long long tq0 = clock64(), tq1; long long qa[8]; int qi = 0;
+#define TLX_Q { tq1 = clock64(); qa[qi++] = tq1 - tq0; tq0 = tq1; }
+#else
+#define TLX_Q
+#endif
   uint32_t kmx = 0, kmn = 0xFFFFFFFFu;
   for (int i = threadIdx.x; i < m; i += blockDim.x) {
     const uint32_t k16 = cand_key(cand[i]) >> 16;
@@ -556,6 +831,7 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
   __syncthreads();
   for (int i = threadIdx.x; i < m; i += blockDim.x) atomicAdd(&win[kmax - (int)(cand_key(cand[i]) >> 16)], 1u);
   __syncthreads();
+  TLX_Q
   const float xmax = key16_value(kmax);
   const int per = (W + (int)blockDim.x - 1) / (int)blockDim.x;
   const int i0 = threadIdx.x * per;
@@ -578,6 +854,7 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
   const int vk_idx = s.tmp_i[0];
   const uint32_t ties_admitted = (uint32_t)s.tmp_i[1], ties_total = (uint32_t)s.tmp_i[2];
 
+  TLX_Q
   // denominator and top-p threshold over the top-k set
   double mass = 0.0;
   for (int j = 0; j < per; ++j) {
@@ -610,6 +887,7 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
   const bool cut_ties = vstar_idx == vk_idx && ties_admitted < ties_total;
   __syncthreads();
 
+  TLX_Q
   // the lowest tokens of the boundary group are the admitted ones: list the group's tokens
   uint32_t* tie_tok = s.hist;   // the histogram is no longer needed
   if (cut_ties) {
@@ -623,6 +901,7 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
   }
   const int n_ties = cut_ties ? s.fill : 0;
 
+  TLX_Q
   // Gumbel arg-max over the kept candidates, screened in f32 (see final_argmax)
   const int64_t nrow = row + p.dim0_offset;
   float a1 = -INFINITY, a2 = -INFINITY, q1 = 0.f, u1 = 0.5f;
@@ -636,16 +915,32 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
     for (int j = 0; j < n_ties; ++j) rank += tie_tok[j] < tok ? 1u : 0u;
     return rank < ties_admitted;
   };
-  for (int i = threadIdx.x; i < m; i += blockDim.x) {
-    const uint64_t c = cand[i];
-    if (kept(c)) {
-      const float u = p.noise.at(nrow, (int64_t)cand_low(c));
-      const float q = __fdiv_rn(key_f32(cand_key(c)), T_);
-      const float a = q + gumbel_fast(u);
-      if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = u; c1 = (int)cand_low(c); }
-      else if (a > a2) a2 = a;
+  {
+    // first decide which of the thread's candidates are kept and start all their noise loads
+    constexpr int kPerMax = kMergeCap / kThreads;   // the smaller of the two kernels' block sizes bounds it
+    uint32_t keep_mask = 0;
+    float uu[kPerMax];
+#pragma unroll
+    for (int j = 0; j < kPerMax; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      uu[j] = 0.5f;
+      if (i < m) {
+        const uint64_t c = cand[i];
+        if (kept(c)) { keep_mask |= 1u << j; uu[j] = p.noise.at(nrow, (int64_t)cand_low(c)); }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kPerMax; ++j) {
+      if (keep_mask & (1u << j)) {
+        const uint64_t c = cand[threadIdx.x + j * blockDim.x];
+        const float q = __fdiv_rn(key_f32(cand_key(c)), T_);
+        const float a = q + gumbel_fast(uu[j]);
+        if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = uu[j]; c1 = (int)cand_low(c); }
+        else if (a > a2) a2 = a;
+      }
     }
   }
+  TLX_Q
   const Best top = block_best(Best{a1, c1}, s);
   const float cut = top.y - (kGumbelSlack + 1e-5f * fabsf(top.y));
   const int crowded = __syncthreads_or(a2 >= cut);
@@ -662,7 +957,14 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
       }
     }
   }
-  return block_best(best, s).tok;
+  TLX_Q
+  const int result = block_best(best, s).tok;
+#ifdef TLX_PROFILE
+  TLX_Q
+  if (threadIdx.x == 0 && (blockIdx.x % 61) == 0)
+    printf("tail m %d W %d ties %d cut %d crowded %d | hist %lld boundary %lld mass %lld tielist %lld screen %lld decide %lld best %lld\n", m, W, n_ties, (int)cut_ties, crowded, qa[0], qa[1], qa[2], qa[3], qa[4], qa[5], qa[6]);
+#endif
+  return result;
 }
 
 template <int DT>
@@ -691,49 +993,74 @@ __device__ __forceinline__ int merge_row_fast(const SampleParams& p, int64_t row
 }
 
 __device__ __forceinline__ int merge_row_general_bf16(const SampleParams& p, int64_t row, int K, float pp, float T_,
-                                                      SelectShared& s, uint32_t* win) {
+                                                      SelectShared& s, uint32_t* win, bool threshold_only = false) {
   const __nv_bfloat16* rowp = reinterpret_cast<const __nv_bfloat16*>(p.logits) + row * p.row_stride;
   if (threadIdx.x == 0) s.tmp_i[0] = 0;
+  for (int i = threadIdx.x; i < kWin; i += blockDim.x) win[i] = 0;
   __syncthreads();
   float smax = 0.f;
-  double mass = 0.0;
+  double below = 0.0;
   if ((int)threadIdx.x < p.S) {
     const SliceHeader* h = record_header(p, row, threadIdx.x);
     const int k = ld_cg(&h->kmax16);
     s.hist[256 + threadIdx.x] = (uint32_t)k;
     atomicMax(&s.tmp_i[0], k);
     smax = ld_cg(&h->smax);
-    mass = ld_cg(&h->mass);
+    below = ld_cg(&h->mass);
   }
   __syncthreads();
   const int kmax = s.tmp_i[0];
   const float xmax = key16_value(kmax);
-  double term = ((int)threadIdx.x < p.S) ? mass * (double)expf(smax - xmax) : 0.0;
-  double Z;
-  block_scan_incl<double>(term, s.scan_f64, &Z, ShflUpF64());
-  // window anchored at the row maximum = shifted sum of the slices' windows
-  for (int idx = threadIdx.x; idx < kWin; idx += blockDim.x) {
-    uint32_t acc = 0;
-    for (int sl = 0; sl < p.S; ++sl) {
-      const int j = idx - (kmax - (int)s.hist[256 + sl]);
-      if (j >= 0) {
-        const uint32_t w = ld_cg(reinterpret_cast<const uint32_t*>(record_payload(p, row, sl)) + (j >> 1));
-        acc += (j & 1) ? (w >> 16) : (w & 0xFFFFu);
+  // mass below the row's window: the slices' below-window sums, rescaled to the row maximum ...
+  double part = ((int)threadIdx.x < p.S) ? below * (double)expf(smax - xmax) : 0.0;
+  // ... plus whatever of a slice's window hangs out below the row's.  The windows are added up
+  // shifted by (row max - slice max); 16-byte loads, several in flight per thread.
+  constexpr int kVecPerSlice = kWin / 8;   // 8 counts per 16-byte vector
+  const int nv = p.S * kVecPerSlice;
+  for (int v0 = threadIdx.x; v0 < nv; v0 += 4 * blockDim.x) {
+    uint4 r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * blockDim.x;
+      r[u] = make_uint4(0, 0, 0, 0);
+      if (v < nv)
+        r[u] = ld_cg(reinterpret_cast<const uint4*>(record_payload(p, row, v / kVecPerSlice)) + (v % kVecPerSlice));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * blockDim.x;
+      if (v >= nv) continue;
+      const int sl = v / kVecPerSlice;
+      const int shift = kmax - (int)s.hist[256 + sl];
+      const uint32_t w4[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t c = (j & 1) ? (w4[j >> 1] >> 16) : (w4[j >> 1] & 0xFFFFu);
+        if (c) {
+          const int idx = (v % kVecPerSlice) * 8 + j + shift;
+          if (idx < kWin) atomicAdd(&win[idx], c);
+          else if (kmax - idx >= 0) part += (double)c * (double)expf(key16_value(kmax - idx) - xmax);
+        }
       }
     }
-    win[idx] = acc;
   }
   __syncthreads();
+  // denominator over the whole row = mass inside the window (from the counts) + mass below it
+  for (int i = threadIdx.x; i < kWin; i += blockDim.x) {
+    const uint32_t c = win[i];
+    if (c && kmax - i >= 0) part += (double)c * (double)expf(key16_value(kmax - i) - xmax);
+  }
+  double Z;
+  block_scan_incl<double>(part, s.scan_f64, &Z, ShflUpF64());
   RowPreset pre;
   pre.top = ((uint64_t)key16_to_key32((uint32_t)kmax) << 32) | 1ull;
   pre.have_window = true;
   pre.mass = Z;
+  pre.threshold_only = threshold_only;
   return general_row_bf16<kWin>(rowp, p.vocab, K, pp, T_, p.noise, row + p.dim0_offset, s, win, pre);
 }
 
 // ---- the kernels --------------------------------------------------------------------------
-constexpr size_t kSharedHeader = (sizeof(SelectShared) + 15) & ~size_t(15);
-constexpr size_t kUnionBytes = 32768;  // kMergeCap u64 == kWin u32 == kHistBins f64
 constexpr size_t kSlicesSmem = kSharedHeader + kUnionBytes + 2 * (size_t)kSliceBytes + sizeof(Control);
 constexpr size_t kMergeSmem = kSharedHeader + kUnionBytes;
 
@@ -761,7 +1088,6 @@ __global__ void __launch_bounds__(kThreads, 2) sample_slices_kernel(SampleParams
 
   const Geometry g{p.S, p.chunk_elems, p.nchunks, p.vocab, 31 - __clz(p.chunk_elems), p.div_magic};
   const int total = (int)(p.rows * p.S);
-  const bool planned = p.rows <= kPlanRows;
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl.mbar[0], 1);
@@ -769,105 +1095,137 @@ __global__ void __launch_bounds__(kThreads, 2) sample_slices_kernel(SampleParams
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.timeout = 0;
   }
-  // Plan (small batches): rows whose merge is long (top-k disabled or large) come first, the
-  // others follow in reverse order; class and top-k of every row are kept in shared memory.
-  if (planned) {
-    constexpr int kPer = kPlanRows / kThreads;
-    uint32_t flags[kPer], packed = 0;
+  __syncthreads();
+  auto load = [&](int item, int b) {
+    if (item < total && warp_id() == 0) {
+      const int rp = g.div_S(item);
+      issue_slice_load<DT>(p, g, rp, item - rp * p.S, slice_base + (size_t)b * kSliceBytes, &ctl.mbar[b]);
+    }
+  };
+  // Row parameters are fetched one slice ahead, so that the per-slice path never waits for them:
+  // packed as top-k in the low bits, bit 30 = greedy, bit 31 = general.
+  auto fetch_class = [&](int item) -> uint32_t {
+    if (item >= total) return 0u;
+    int K;
+    const int cls = classify_row(p, g.div_S(item), K);
+    return cls == kGreedy ? (1u << 30)
+           : cls == kGeneral ? ((1u << 31) | ((int64_t)K >= p.vocab ? (1u << 29) : 0u))
+                             : (uint32_t)K;
+  };
+
+  // Work list.  Small batches of general rows (only_general): every CTA first compacts the wanted
+  // rows into shared memory (each thread classifies a few rows, one block scan), so that the
+  // items (wanted row, slice) can be dealt out evenly: CTA c takes the items c, c + grid, ...
+  // Otherwise the items are simply (row, slice) = (i / S, i % S) over all rows.
+  constexpr int kPlanRows = 4 * kThreads;
+  static_assert(kPlanRows <= 1024, "rows_list holds 1024 rows");
+  const bool compact = p.only_general && p.rows <= kPlanRows;
+  int n_items = total;
+  if (compact) {
+    uint32_t flags = 0, cnt = 0;
 #pragma unroll
-    for (int h = 0; h < kPer; ++h) {
-      const int r = threadIdx.x + h * kThreads;
-      flags[h] = 0;
+    for (int h = 0; h < 4; ++h) {
+      const int r = threadIdx.x * 4 + h;
       if (r < p.rows) {
-        int K;
-        const int cls = classify_row(p, r, K);
-        flags[h] = cls == kGeneral ? 1u : 0x10000u;
-        ctl.kk[r] = cls == kGeneral ? (unsigned short)0xFFFF : cls == kGreedy ? (unsigned short)0xFFFE
-                                                                               : (unsigned short)K;
+        const uint32_t packed = fetch_class(r * p.S);
+        if ((packed >> 31) && (!p.final_pass || ((packed >> 29) & 1u))) { flags |= 1u << h; ++cnt; }
       }
-      packed += flags[h];
     }
     uint32_t tot;
-    uint32_t excl = block_scan_incl<uint32_t>(packed, s.scan_u32, &tot, ShflUpU32()) - packed;
+    uint32_t pos = block_scan_incl<uint32_t>(cnt, s.scan_u32, &tot, ShflUpU32()) - cnt;
+    unsigned short* rows_list = ctl.rows_list;
 #pragma unroll
-    for (int h = 0; h < kPer; ++h) {
-      const int r = threadIdx.x + h * kThreads;
-      if (r < p.rows) {
-        const int pos = (flags[h] & 1u) ? (int)(excl & 0xFFFFu) : (int)p.rows - 1 - (int)(excl >> 16);
-        ctl.order[pos] = (unsigned short)r;
-      }
-      excl += flags[h];
-    }
+    for (int h = 0; h < 4; ++h)
+      if (flags & (1u << h)) rows_list[pos++] = (unsigned short)(threadIdx.x * 4 + h);
+    n_items = (int)tot * p.S;
+    __syncthreads();
   }
-  __syncthreads();
-  auto row_of = [&](int item) -> int64_t {
-    const int rp = g.div_S(item);
-    return planned ? (int64_t)ctl.order[rp] : (int64_t)rp;
-  };
-  auto class_of = [&](int64_t row, int& K) {
-    if (!planned) return classify_row(p, row, K);
-    const unsigned short v = ctl.kk[row];
-    K = v;
-    return v == 0xFFFE ? (int)kGreedy : v == 0xFFFF ? (int)kGeneral : (int)kFast;
-  };
-  auto load = [&](int item, int b) {
-    if (item < total && warp_id() == 0)
-      issue_slice_load<DT>(p, g, row_of(item), item - g.div_S(item) * p.S, slice_base + (size_t)b * kSliceBytes,
-                           &ctl.mbar[b]);
-  };
-
   const int stride = gridDim.x;
-  int cur = blockIdx.x, nxt = cur + stride;
-  int b = 0;
+  const int n_my = (int)blockIdx.x < n_items ? (n_items - 1 - (int)blockIdx.x) / stride + 1 : 0;
   uint32_t phases = 0;   // bit i: parity to wait for on barrier i
-  load(cur, 0);
-  load(nxt, 1);
-  // One block-wide barrier per slice in the common case: warps reduce their share of the slice
-  // on their own, then meet once; after that warp 0 refills the buffer and the last thread
-  // writes the record's header while everybody else already waits for the next slice.
-  while (cur < total) {
-    unsigned char* buf = slice_base + (size_t)b * kSliceBytes;
-    if (!mbar_wait(&ctl.mbar[b], (phases >> b) & 1u)) ctl.timeout = 1;
-    phases ^= 1u << b;
-
-    const int64_t row = row_of(cur);
-    const int sl = cur - g.div_S(cur) * p.S;
-    const int elems = g.slice_elems(sl);
-    int K;
-    const int cls = class_of(row, K);
-    WarpResults& wr = ctl.wr[b];
-    if (cls == kGreedy) {
-      reduce_slice_greedy<DT>(buf, elems, wr);
-    } else if (cls == kFast) {
-      uint64_t* segment = reinterpret_cast<uint64_t*>(record_payload(p, row, sl)) + warp_id() * kWarpCap;
-      reduce_slice_fast<DT>(g, sl, K, buf, elems, segment, reinterpret_cast<unsigned short*>(uni) + warp_id() * kWarpHits,
-                            wr);
-    } else if constexpr (DT == TLX_BF16) {
-      reduce_slice_general_bf16(p, g, row, sl, buf, elems, s, win);
-    }
-    __syncthreads();   // the slice is reduced and its buffer is free
-    load(nxt + stride, b);
-    if (threadIdx.x == kPublisher) {
-      SliceHeader* hdr = record_header(p, row, sl);
-      if (cls == kGreedy) {
-        unsigned long long best = 0;
-        for (int w = 0; w < kWarps; ++w) best = wr.top[w] > best ? wr.top[w] : best;
-        const int q = 0x7FFFFFFF - (int)(uint32_t)best;
-        const int64_t col = elems > 0 ? g.column(sl, q) : 0;
-        hdr->top = (best & 0xFFFFFFFF00000000ull) | (uint32_t)(0x7FFFFFFF - (int32_t)col);
-      } else if (cls == kFast) {
-        int over = 0;
-        for (int w = 0; w < kWarps; ++w) { hdr->wcount[w] = wr.count[w]; over |= wr.overflow[w]; }
-        hdr->cutoff_bin = wr.cutoff_bin;
-        hdr->overflow = over;
+  for (int base = 0; base < n_my; base += 64) {
+    if (threadIdx.x == 0) ctl.list_n = 0;
+    __syncthreads();
+    if (threadIdx.x < 64 && base + (int)threadIdx.x < n_my) {
+      int item = blockIdx.x + (base + threadIdx.x) * stride;
+      if (compact) {   // (wanted row index, slice) -> (row, slice)
+        const int wi = g.div_S(item);
+        item = (int)ctl.rows_list[wi] * p.S + (item - wi * p.S);
+      }
+      const uint32_t packed = fetch_class(item);
+      // general rows only when asked; the final pass further wants the top-k filter to be disabled
+      if ((!p.only_general || (packed >> 31)) && (!p.final_pass || ((packed >> 29) & 1u))) {
+        const int pos = atomicAdd(&ctl.list_n, 1);
+        ctl.list[pos] = item;
+        ctl.list_cls[pos] = packed;
       }
     }
-    cur = nxt;
-    nxt += stride;
-    b ^= 1;
+    __syncthreads();
+    const int nl = ctl.list_n;
+    if (nl > 0) load(ctl.list[0], 0);
+    if (nl > 1) load(ctl.list[1], 1);
+    // One block-wide barrier per slice in the common case: warps reduce their share of the slice
+    // on their own, then meet once; after that warp 0 refills the buffer and the last thread
+    // writes the record's header while everybody else already waits for the next slice.
+    for (int j = 0; j < nl; ++j) {
+      const int b = j & 1;
+      unsigned char* buf = slice_base + (size_t)b * kSliceBytes;
+      const int cur = ctl.list[j];
+      const uint32_t cls_cur = ctl.list_cls[j];
+      if (!mbar_wait(&ctl.mbar[b], (phases >> b) & 1u)) ctl.timeout = 1;
+      phases ^= 1u << b;
+
+      const int64_t row = g.div_S(cur);
+      const int sl = cur - (int)row * p.S;
+      const int elems = g.slice_elems(sl);
+      const int cls = (cls_cur >> 30) & 1u ? (int)kGreedy : (cls_cur >> 31) ? (int)kGeneral : (int)kFast;
+      const int K = (int)(cls_cur & 0x1FFFFFFFu);
+      WarpResults& wr = ctl.wr[b];
+      if (p.final_pass) {
+        if constexpr (DT == TLX_BF16) reduce_slice_final_bf16(p, g, row, sl, buf, elems, s, uni);
+      } else if (cls == kGreedy) {
+        reduce_slice_greedy<DT>(buf, elems, wr);
+      } else if (cls == kFast) {
+        uint64_t* segment = reinterpret_cast<uint64_t*>(record_payload(p, row, sl)) + warp_id() * kWarpCap;
+        reduce_slice_fast<DT>(g, sl, K, buf, elems, segment,
+                              reinterpret_cast<unsigned short*>(uni) + warp_id() * kWarpHits, wr);
+      } else if constexpr (DT == TLX_BF16) {
+        reduce_slice_general_bf16(p, g, row, sl, buf, elems, s, win);
+      }
+      __syncthreads();   // the slice is reduced and its buffer is free
+      if (j + 2 < nl) load(ctl.list[j + 2], b);
+      if (p.final_pass) {
+        // count the slice on its row; whoever delivers the last one turns the row's best into its token
+        if (threadIdx.x == kPublisher) {
+          RowState* rs = p.rowstate + row;
+          __threadfence();
+          if (atomicAdd(&rs->done, 1) == p.S - 1) {
+            __threadfence();
+            const unsigned long long best = atomicMax(&rs->best, 0ull);
+            p.out_tokens[row] = 0x7FFFFFFF - (int32_t)(uint32_t)best;
+          }
+        }
+      } else if (threadIdx.x == kPublisher) {
+        SliceHeader* hdr = record_header(p, row, sl);
+        if (cls == kGreedy) {
+          unsigned long long best = 0;
+          for (int w = 0; w < kWarps; ++w) best = wr.top[w] > best ? wr.top[w] : best;
+          const int q = 0x7FFFFFFF - (int)(uint32_t)best;
+          const int64_t col = elems > 0 ? g.column(sl, q) : 0;
+          hdr->top = (best & 0xFFFFFFFF00000000ull) | (uint32_t)(0x7FFFFFFF - (int32_t)col);
+        } else if (cls == kFast) {
+          int over = 0;
+          for (int w = 0; w < kWarps; ++w) { hdr->wcount[w] = wr.count[w]; over |= wr.overflow[w]; }
+          hdr->cutoff_bin = wr.cutoff_bin;
+          hdr->overflow = over;
+        }
+      }
+    }
+    __syncthreads();
   }
   if (threadIdx.x == 0 && ctl.timeout) atomicOr(&p.counters[1], 1);
 }
+
 
 // Kernel 2: one CTA per row turns the row's slice records into a token.
 template <int DT>
@@ -894,6 +1252,183 @@ __global__ void __launch_bounds__(kRowThreads) sample_merge_kernel(SampleParams 
     if (p.counters[1]) status |= kStatusTimeout;
     p.out_tokens[row] = tok;
     if (p.out_status) p.out_status[row] = status;
+  }
+}
+
+// ---- one CTA per row ---------------------------------------------------------------------------
+// For batches of at least one row per CTA slot the row is not cut up: a CTA streams its row
+// through the two slice buffers tile by tile (one contiguous bulk copy each) and keeps the
+// selection state of collect_row in shared memory across the tiles -- a 4096-bin histogram of
+// what was collected, the candidate list, and the threshold bin, which rises as soon as the
+// histogram shows K collected elements at or above a higher bin.  After the first tile the
+// per-tile work is one packed compare per two elements; everything (candidates, tail, token)
+// stays inside the CTA, so there is no workspace traffic and no second kernel.
+constexpr size_t kRowsSmem = kSharedHeader + kUnionBytes + 2 * (size_t)kSliceBytes + sizeof(Control);
+
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p) {
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
+  unsigned char* uni = smem_raw + kSharedHeader;
+  unsigned char* slice_base = uni + kUnionBytes;
+  Control& ctl = *reinterpret_cast<Control*>(uni + kUnionBytes + 2 * (size_t)kSliceBytes);
+  uint64_t* cand = reinterpret_cast<uint64_t*>(uni);
+  uint32_t* win = reinterpret_cast<uint32_t*>(uni);
+  double* massbins = reinterpret_cast<double*>(uni);
+  // while a row is collected its histogram area is idle and holds the warps' hit lists
+  unsigned short* hits = reinterpret_cast<unsigned short*>(s.hist) + warp_id() * (kHistBins * 2 / kWarps);
+
+  // The tiles of a row are its S interleaved slices: every tile is a sample of the whole row,
+  // so the threshold estimated on the first one is already right for the others.
+  const Geometry g{p.S, p.chunk_elems, p.nchunks, p.vocab, 31 - __clz(p.chunk_elems), p.div_magic};
+  const int64_t n = p.vocab;
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl.mbar[0], 1);
+    mbar_init(&ctl.mbar[1], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    ctl.timeout = 0;
+  }
+  __syncthreads();
+  uint32_t phases = 0;
+
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T* rowp = reinterpret_cast<const T*>(p.logits) + row * p.row_stride;
+    auto load = [&](int t, int b) {
+      if (t < p.S && warp_id() == 0)
+        issue_slice_load<DT>(p, g, row, t, slice_base + (size_t)b * kSliceBytes, &ctl.mbar[b]);
+    };
+    int K;
+    const int cls = classify_row(p, row, K);
+    const float pp = p.top_p[row], T_ = p.temperature[row];
+    int status = 0, tok = 0;
+    // rows without top-k only get their threshold here: the final pass is the third kernel's
+    const bool deferred = DT == TLX_BF16 && cls == kGeneral && (int64_t)K >= n && p.have_records;
+    if (!deferred) {
+      load(0, 0);
+      load(1, 1);
+    }
+
+    if (cls == kGeneral) {
+      status = kStatusGeneral;
+      bool done = false;
+      if constexpr (DT == TLX_BF16) {
+        if (deferred) {
+          // The slices kernel left this row's histograms in the workspace; they give the top-p
+          // threshold, which goes to the row's state for the final pass.
+          const int vstar16 = merge_row_general_bf16(p, row, K, pp, T_, s, win, true);
+          if (threadIdx.x == 0) {
+            RowState* rs = p.rowstate + row;
+            rs->min_key = vstar16 == 0 ? 0u : key16_to_key32((uint32_t)vstar16);
+            rs->thr = vstar16 == 0 ? -INFINITY : key16_value(vstar16);
+            rs->best = 0ull;
+            rs->done = 0;
+            if (p.out_status) p.out_status[row] = status;
+          }
+          __syncthreads();
+          continue;
+        }
+      }
+      if (!done) {
+        // drain the two copies that are in flight, then take the whole-row path from global memory
+        for (int t = 0; t < 2 && t < p.S; ++t) {
+          if (!mbar_wait(&ctl.mbar[t], (phases >> t) & 1u)) ctl.timeout = 1;
+          phases ^= 1u << t;
+        }
+        __syncthreads();
+        if constexpr (DT == TLX_BF16) {
+          RowPreset pre;
+          tok = general_row_bf16<kWin>(rowp, n, K, pp, T_, p.noise, row + p.dim0_offset, s, win, pre);
+        } else {
+          tok = general_row_radix<DT>(rowp, n, K, pp, T_, p.noise, row + p.dim0_offset, s, massbins);
+        }
+      }
+    } else {
+      if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
+      unsigned long long wbest = 0;   // greedy: this warp's running arg-max (key << 32 | 0x7FFFFFFF - column)
+      __syncthreads();
+      for (int t = 0; t < p.S; ++t) {
+        const int b = t & 1;
+        unsigned char* buf = slice_base + (size_t)b * kSliceBytes;
+        const int elems = g.slice_elems(t);
+        if (!mbar_wait(&ctl.mbar[b], (phases >> b) & 1u)) ctl.timeout = 1;
+        phases ^= 1u << b;
+        if (cls == kGreedy) {
+          reduce_slice_greedy<DT>(buf, elems, ctl.wr[b]);
+          if (lane_id() == 0) {
+            const unsigned long long v = ctl.wr[b].top[warp_id()];
+            if (v) {
+              const int64_t col = g.column(t, 0x7FFFFFFF - (int)(uint32_t)v);
+              const unsigned long long c = (v & 0xFFFFFFFF00000000ull) | (uint32_t)(0x7FFFFFFF - (int32_t)col);
+              wbest = c > wbest ? c : wbest;
+            }
+          }
+        } else {
+          if (t == 0) {
+            // First threshold, from the maxima of the threads' elements: aim at 1.3 K + 32 elements of
+            // the ROW, i.e. that fraction of this tile.  Too high an estimate is caught at the end
+            // (fewer than K candidates), too low a one by the refinement below.
+            const int nvec = elems / VEC;
+            const float frac = fminf(1.f, (1.3f * (float)K + 32.f) / (float)n);
+            const int vec_per_thread = (nvec + (int)blockDim.x - 1) / (int)blockDim.x;
+            int vecs = (int)(0.7f / (frac * VEC) + 0.5f);
+            vecs = vecs < 1 ? 1 : (vecs > vec_per_thread ? vec_per_thread : vecs);
+            const uint32_t tkey = thread_max_key<DT>(buf, nvec, vecs);
+            const int my_bin = ((int)threadIdx.x < nvec) ? (int)(tkey >> kHistShift) : -1;
+            const int holders = nvec < (int)blockDim.x ? nvec : (int)blockDim.x;
+            int want = (int)((float)holders * (1.f - __expf(-(float)(vecs * VEC) * frac)) + 0.999f);
+            want = want < 1 ? 1 : want;
+            const int b0 = (frac >= 0.5f || nvec == 0) ? 0 : vote_threshold_bin(my_bin, want);
+            if (threadIdx.x == 0) s.bin = b0;
+            __syncthreads();
+          }
+          collect_tile<DT>(buf, elems, s.bin, s, cand, hits, [&](int q) { return g.column(t, q); });
+        }
+        __syncthreads();   // the tile is consumed, its buffer is free
+        load(t + 2, b);
+        // The threshold only has to rise when the candidate list fills up (and once at the end for
+        // the sorting tail, which wants few candidates).
+        if (cls == kFast && s.fill <= kMergeCap &&
+            (s.fill > kMergeCap / 2 || (t == p.S - 1 && DT != TLX_BF16 && s.fill > 2 * K + 64)))
+          refine_candidates(s, cand, K);
+      }
+      if (cls == kGreedy) {
+        unsigned long long* slot = reinterpret_cast<unsigned long long*>(s.scan_f64);
+        if (lane_id() == 0) slot[warp_id()] = wbest;
+        __syncthreads();
+        unsigned long long best = 0;
+        for (int w = 0; w < kWarps; ++w) best = slot[w] > best ? slot[w] : best;
+        tok = 0x7FFFFFFF - (int32_t)(uint32_t)best;
+        __syncthreads();
+      } else {
+        int m = s.fill;
+        __syncthreads();
+        if (m > kMergeCap || m < K) {   // overflow (huge tie groups) or an estimate that was too high: exact select
+          exact_select_row<DT>(rowp, n, K, s, cand);
+          m = K;
+          status |= kStatusRedone;
+          __syncthreads();
+        }
+        tok = -1;
+        if constexpr (DT == TLX_BF16) tok = tail_bf16_hist(p, row, K, pp, T_, m, s, cand);
+        if (tok < 0) {
+          __syncthreads();
+          sort_candidates(cand, m);
+          const int64_t nrow = row + p.dim0_offset;
+          tok = sample_tail<4>(
+              K, pp, T_, s, [&](int i) { return key_f32(cand_key(cand[i])); },
+              [&](int i) { return (int)cand_low(cand[i]); },
+              [&](int i) { return p.noise.at(nrow, (int64_t)cand_low(cand[i])); });
+        }
+      }
+    }
+    if (threadIdx.x == 0) {
+      if (ctl.timeout) status |= kStatusTimeout;
+      p.out_tokens[row] = tok;
+      if (p.out_status) p.out_status[row] = status;
+    }
+    __syncthreads();
   }
 }
 
@@ -1086,7 +1621,8 @@ static SliceLayout slice_layout(int64_t vocab, int elem_bytes) {
   l.S = (l.nchunks + kChunksPerSlice - 1) / kChunksPerSlice;
   return l;
 }
-static size_t counters_bytes(int64_t rows) { return (((size_t)rows + 2) * sizeof(int32_t) + 255) & ~size_t(255); }
+// workspace: [flags | one RowState per row | one record per (row, slice)]
+static size_t counters_bytes(int64_t rows) { return 256 + (((size_t)rows * sizeof(RowState) + 255) & ~size_t(255)); }
 
 }  // namespace tlx
 
@@ -1134,14 +1670,39 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
   // bulk copies need 16-byte aligned row starts and a row length that is a multiple of 16 bytes
   p.use_tma = ((reinterpret_cast<uintptr_t>(logits) & 15) == 0 && ((row_stride * es) & 15) == 0 && ((vocab * es) & 15) == 0) ? 1 : 0;
   p.counters = (int32_t*)workspace;
+  p.rowstate = reinterpret_cast<RowState*>((unsigned char*)workspace + 256);
   p.records = (unsigned char*)workspace + counters_bytes(rows);
 
-  cudaError_t e = cudaMemsetAsync(workspace, 0, counters_bytes(rows), st);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, 256, st);
   if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaMemsetAsync: %s", cudaGetErrorString(e));
   const int64_t items = rows * l.S;
   const int64_t slots = 2ll * device_sm_count();
-  const unsigned grid = (unsigned)(items < slots ? items : slots);
   int rc;
+  if (2 * rows >= slots) {
+    // at least half a row per CTA slot: one CTA per row; only the rows whose top-k is disabled or
+    // large are cut into slices first (their histograms need every SM), by the slices kernel
+    const unsigned grid = (unsigned)(rows < slots ? rows : slots);
+    if (dtype == TLX_BF16) {
+      p.only_general = 1;
+      p.have_records = 1;
+      const unsigned sgrid = (unsigned)(items < slots ? items : slots);
+      if ((rc = ensure_smem((const void*)sample_slices_kernel<TLX_BF16>, kSlicesSmem, "sample")) != TLX_OK) return rc;
+      if ((rc = ensure_smem((const void*)sample_rows_kernel<TLX_BF16>, kRowsSmem, "sample")) != TLX_OK) return rc;
+      sample_slices_kernel<TLX_BF16><<<sgrid, kThreads, kSlicesSmem, st>>>(p);
+      TLX_CHECK_LAUNCH("sample (slices)");
+      sample_rows_kernel<TLX_BF16><<<grid, kThreads, kRowsSmem, st>>>(p);
+      TLX_CHECK_LAUNCH("sample (rows)");
+      p.final_pass = 1;   // rows without top-k: Gumbel arg-max over the kept elements, slice by slice
+      sample_slices_kernel<TLX_BF16><<<sgrid, kThreads, kSlicesSmem, st>>>(p);
+    } else {
+      if ((rc = ensure_smem((const void*)sample_rows_kernel<TLX_F32>, kRowsSmem, "sample")) != TLX_OK) return rc;
+      sample_rows_kernel<TLX_F32><<<grid, kThreads, kRowsSmem, st>>>(p);
+    }
+    TLX_CHECK_LAUNCH("sample (rows)");
+    return TLX_OK;
+  }
+  // small batches: cut the rows into slices so that every SM streams, then merge per row
+  const unsigned grid = (unsigned)(items < slots ? items : slots);
   if (dtype == TLX_BF16) {
     if ((rc = ensure_smem((const void*)sample_slices_kernel<TLX_BF16>, kSlicesSmem, "sample")) != TLX_OK) return rc;
     if ((rc = ensure_smem((const void*)sample_merge_kernel<TLX_BF16>, kMergeSmem, "sample")) != TLX_OK) return rc;

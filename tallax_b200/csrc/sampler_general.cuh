@@ -173,6 +173,7 @@ struct RowPreset {
   uint64_t top = 0;     // row_argmax composite, 0 = unknown
   bool have_window = false;  // win[] already holds the histogram of the window anchored at the row maximum
   double mass = -1.0;   // sum of exp(x - max) over the WHOLE row, < 0 = unknown (used when top-k is disabled)
+  bool threshold_only = false;  // top-k disabled: return the top-p threshold (16-bit key) instead of sampling
 };
 
 // One row, any top-k.  `win` holds WIN uint32 bins; blockDim.x must divide WIN.
@@ -277,6 +278,7 @@ __device__ __forceinline__ int general_row_bf16(const __nv_bfloat16* __restrict_
       cum += total;
     }
   }
+  if (pre.threshold_only && !bounded) return vstar16;
   const uint32_t vstar32 = vstar16 == 0 ? 0u : key16_to_key32((uint32_t)vstar16);
   const bool ordered = bounded && vstar16 == vk16 && ties_admitted < ties_total;
   return final_argmax<TLX_BF16>(row, n, T_, vstar32, bounded, vk32, ties_admitted, ordered, noise, nrow, s);
