@@ -4,17 +4,18 @@ This module is the correctness checker for the CUDA library.  Nothing in the
 product package may import it; only the test-suite, the smoke check and the
 CPU-baseline leg of the benchmark do.
 
-PARITY STATUS: "parity unpinned" against outputs of the reference itself.
-The reference is pure JAX/Pallas-TPU and JAX is not installable here, and the
-reference stores no golden vectors (all its expectations are recomputed through
-jax at test time).  What *is* pinned:
-  * threefry2x32 against the Random123 known-answer vectors that JAX's own
-    test-suite uses (see `THREEFRY_KAT`);
-  * the value-level reference functions that run on a NumPy stand-in for
-    `jax.numpy` (tests/golden/make_golden.py imports them from the reference
-    tree and stores their outputs as fixtures which this oracle must match);
-  * everything else is defined as the NumPy twin of the XLA function the
-    reference's tests compare against (stable sort, take_along_axis, cumsum).
+PARITY STATUS.  The reference is pure JAX/Pallas-TPU, JAX is not installable here and the
+reference stores no golden vectors (its tests recompute every expectation through jax).
+What pins this oracle:
+  * threefry2x32: the Random123 known-answer vectors that JAX's own tests use (`THREEFRY_KAT`);
+  * key transform, cumsum, gather (with out-of-range indices), max_arrays, indexed uniform
+    noise, top_p_mask, top_p_and_sample (token ids) and the sparse categorical draw: outputs
+    of the REFERENCE'S OWN value-level functions, run from the reference checkout with
+    jax.numpy mapped onto NumPy (tests/golden/make_golden.py, fixtures in tests/golden/,
+    checked by tests/test_golden.py);
+  * sort and top-k: "parity unpinned" against reference outputs (their reference code only
+    exists as Pallas kernels); they are defined as the NumPy twins of the XLA functions the
+    reference's tests compare with (stable lexicographic sort; descending stable argsort).
 
 Each function cites the reference file:line it restates (paths inside the
 reference project).
