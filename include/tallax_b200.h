@@ -81,6 +81,26 @@ int tlx_sort(void* stream, const void* keys, int dtype, int64_t rows, int64_t n,
              const int32_t* in_perm, void* out_keys, int32_t* out_perm, void* workspace,
              size_t workspace_bytes);
 
+/* ---- sort without any allocation ------------------------------------------------
+ * Same operation and results as tlx_sort, for callers that have nowhere to get scratch
+ * memory from: code running inside a CUDA-graph capture or a stream callback chain, plugin
+ * hosts whose memory pool is owned by another runtime, or processes that were handed a fixed
+ * memory budget and must not call cudaMalloc (nor have the library call it for them).  The
+ * scratch of the multi-tile path is a fixed area inside the library image (16 MiB, reported by
+ * tlx_sort_static_max_bytes; every GPU that loads the library holds it until exit).
+ *   - rows whose composites need more than that are rejected with TLX_ERR_INVALID and a
+ *     message; nothing is launched;
+ *   - the first call on a device looks up the area's device address (with that device
+ *     current); make that first call before any stream capture;
+ *   - all calls share the one area and it keeps the previous call's contents; the kernels
+ *     write every entry before reading it, so nothing needs clearing, but two calls that
+ *     overlap on the GPU (different streams) race: serialise them;
+ *   - no cudaMalloc, cudaFree or allocating library routine is called.
+ * No counterpart in the reference (its XLA runtime owns all device memory).           */
+size_t tlx_sort_static_max_bytes(void);
+int tlx_sort_static(void* stream, const void* keys, int dtype, int64_t rows, int64_t n, int descending,
+                    const int32_t* in_perm, void* out_keys, int32_t* out_perm);
+
 /* ---- top-k ---------------------------------------------------------------------
  * Row-wise descending top-`k_max` of x[rows, n] (row stride in elements), ties broken
  * by lower index; out_vals keeps the input dtype, out_idx is int32, both [rows, k_max].

@@ -26,6 +26,8 @@ SIGNATURES = {
     "tlx_argmax": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _vp]),
     "tlx_sort_workspace_bytes": (_sz, [_i64, _i64]),
     "tlx_sort": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _vp, _vp, _vp, _vp, _sz]),
+    "tlx_sort_static_max_bytes": (_sz, []),
+    "tlx_sort_static": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _vp, _vp, _vp]),
     "tlx_top_k_workspace_bytes": (_sz, [_i64, _i64, _i32]),
     "tlx_top_k": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _f64, _i32, _vp, _vp, _vp, _vp, _vp,
                          _vp, _sz]),

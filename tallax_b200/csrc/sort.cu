@@ -171,6 +171,10 @@ static int sort_dispatch(cudaStream_t st, const void* keys, int64_t rows, int64_
   return TLX_OK;
 }
 
+// Scratch of tlx_sort_static: lives in the library's image on every GPU that loads it.
+constexpr size_t kStaticSortBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticSortBytes];
+
 }  // namespace tlx
 
 using namespace tlx;
@@ -201,6 +205,35 @@ int tlx_sort(void* stream, const void* keys, int dtype, int64_t rows, int64_t n,
     case TLX_U32: return sort_dispatch<TLX_U32>(st, keys, rows, n, descending, in_perm, out_keys, out_perm, workspace, workspace_bytes);
     default: return set_error(TLX_ERR_UNSUPPORTED, "sort: dtype %d not supported", dtype);
   }
+}
+
+size_t tlx_sort_static_max_bytes(void) { return kStaticSortBytes; }
+
+int tlx_sort_static(void* stream, const void* keys, int dtype, int64_t rows, int64_t n, int descending,
+                    const int32_t* in_perm, void* out_keys, int32_t* out_perm) {
+  // The size check comes first and touches no CUDA state.
+  const size_t need = tlx_sort_workspace_bytes(rows, n);
+  if (need > kStaticSortBytes)
+    return set_error(TLX_ERR_INVALID,
+                     "sort_static: %lld rows of %lld keys need %zu bytes of scratch, the built-in area holds %zu; "
+                     "use tlx_sort with a caller-provided workspace",
+                     (long long)rows, (long long)n, need, (size_t)kStaticSortBytes);
+  // In host code the array's name is only a handle: the device address is looked up once per
+  // device (with that device current) and remembered.
+  static void* device_address[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "sort_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return set_error(TLX_ERR_UNSUPPORTED, "sort_static: device ordinal %d not supported", dev);
+  if (!device_address[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_sort_scratch);
+    if (e != cudaSuccess || !ptr)
+      return set_error(TLX_ERR_CUDA, "sort_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    device_address[dev] = ptr;
+  }
+  return tlx_sort(stream, keys, dtype, rows, n, descending, in_perm, out_keys, out_perm, device_address[dev],
+                  kStaticSortBytes);
 }
 
 }  // extern "C"
