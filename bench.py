@@ -26,6 +26,7 @@ if ROOT not in sys.path:
 B, V = 256, 128256          # benchmark configuration: decode batch and vocabulary (Llama-3 sized)
 N_SETS = 4                  # rotating input sets: 4 x 65.7 MB of logits > 126 MB L2, so every step reads HBM
 ALGO_BYTES = B * V * 2 + B * 12 + B * 4   # logits once + three parameter vectors + tokens out
+NCU_TRAFFIC_BYTES = None    # dram__bytes_read.sum + dram__bytes_write.sum over one call's kernels (profiles/)
 METRIC, UNIT = "sampled_tokens_per_s", "tokens/s"
 WORKLOAD = ("fused temperature/top-k/top-p/noise sampling, bf16 logits [256,128256] = N(0,sigma=3) + 10 at 8 "
             "columns per row, T~U[0.5,1.5], top_k~U{1..1024} with 10% disabled, top_p~U[0.6,1), explicit f32 "
@@ -189,13 +190,16 @@ def run_ours(args):
         step(i)
     barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    lib = _lib.load()
     with ClockSampler(local_rank) as clocks:
         time.sleep(0.15)
         barrier()
+        launches0 = lib.tlx_kernel_launches()
         start.record()
         for i in range(args.steps):
             step(i)
         stop.record()
+        launches = lib.tlx_kernel_launches() - launches0
         barrier()
         time.sleep(0.1)
     ms = start.elapsed_time(stop)
@@ -263,11 +267,13 @@ def run_ours(args):
             "e2e": {"value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
                     "h2d_bytes_per_step": B * V * 2 + B * V * 4 + B * 12, "d2h_bytes_per_step": B * 4,
                     "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
-                         "note": "algorithmic bytes of one sampler call / mean duration of the call's two kernels "
-                                 "(fast kernel + general kernel), CUDA events on the launching stream"},
+                         "traffic": NCU_TRAFFIC_BYTES, "peak_source": peak_src,
+                         "note": "algorithmic bytes of one sampler call / mean duration of the whole call (all of its "
+                                 f"{launches // max(args.steps, 1)} kernels, which together read the logits once), "
+                                 "CUDA events on the launching stream; traffic = dram read+write of the call's "
+                                 "kernels from one ncu capture of this workload"},
             "cpu_baseline": {"value": n_cpu / cpu_dt, "unit": UNIT, "cores": 1, "kind": "port",
                              "sample": f"first {n_cpu} rows of input set 0, NumPy restatement of the reference "
                                        f"(JAX not installable here); {mismatches} token mismatches vs the GPU "

@@ -44,6 +44,9 @@ typedef enum {
 
 int tlx_abi_version(void);
 const char* tlx_last_error(void);
+/* Number of kernels this library has launched in the process so far (diagnostic: lets a
+ * benchmark count launches per call instead of assuming them). */
+unsigned long long tlx_kernel_launches(void);
 
 /* ---- gather --------------------------------------------------------------------
  * out[b,j] = values[b, idx[b,j]] (axis 1) or out[i,b] = values[idx[i,b], b] (axis 0);

@@ -21,6 +21,7 @@ _vp, _i64, _i32, _u32, _f32, _f64, _sz = (C.c_void_p, C.c_int64, C.c_int, C.c_ui
 SIGNATURES = {
     "tlx_abi_version": (_i32, []),
     "tlx_last_error": (C.c_char_p, []),
+    "tlx_kernel_launches": (C.c_ulonglong, []),
     "tlx_take_along_axis": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32]),
     "tlx_cumsum": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32]),
     "tlx_argmax": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _vp]),

@@ -76,7 +76,9 @@ def sample_vocab_sharded(rng_key, logits_shard, tpu_sampling_metadata, *, group=
                                  vocab_total=v_local * world, dim0_offset=dim0_offset)
     gathered = torch.empty((world,) + tuple(block.shape), dtype=block.dtype, device=block.device)
     if world > 1:
-        dist.all_gather_into_tensor(gathered, block, group=group)
+        # concatenated-along-dim-0 form: the one every backend accepts
+        dist.all_gather_into_tensor(gathered.view((world * block.shape[0],) + tuple(block.shape[1:])), block,
+                                    group=group)
     else:
         gathered[0].copy_(block)
     return ops.merge_and_sample(gathered, md.top_k, md.top_p, md.temperature)

@@ -2,6 +2,8 @@
 // All four are plain HBM-bound streaming kernels: one read, one write, coalesced.
 #include "tlx_common.cuh"
 
+#include <atomic>
+
 namespace tlx {
 
 static thread_local char g_err[512] = "";
@@ -13,6 +15,9 @@ int set_error(int code, const char* fmt, ...) {
   va_end(ap);
   return code;
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 // ---------------------------------------------------------------------------------
 // gather
@@ -212,6 +217,7 @@ extern "C" {
 
 int tlx_abi_version(void) { return TLX_ABI_VERSION; }
 const char* tlx_last_error(void) { return tlx::g_err; }
+unsigned long long tlx_kernel_launches(void) { return tlx::g_launches.load(std::memory_order_relaxed); }
 
 int tlx_take_along_axis(void* stream, const void* values, const int32_t* indices, void* out, int64_t val_rows,
                         int64_t val_cols, int64_t idx_rows, int64_t idx_cols, int elem_bytes, int axis) {

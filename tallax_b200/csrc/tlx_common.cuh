@@ -15,6 +15,7 @@ namespace tlx {
 
 // ---- host-side error plumbing ------------------------------------------------
 int set_error(int code, const char* fmt, ...);
+void count_launch();   // bumps the process-wide launch counter read by tlx_kernel_launches()
 
 #define TLX_CHECK_ARG(cond, ...)                               \
   do {                                                         \
@@ -23,6 +24,7 @@ int set_error(int code, const char* fmt, ...);
 
 #define TLX_CHECK_LAUNCH(what)                                                         \
   do {                                                                                 \
+    ::tlx::count_launch();                                                             \
     cudaError_t e_ = cudaGetLastError();                                               \
     if (e_ != cudaSuccess)                                                             \
       return ::tlx::set_error(TLX_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e_));    \

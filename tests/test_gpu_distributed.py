@@ -1,0 +1,65 @@
+"""Two-GPU run of the vocab-sharded sampler over NCCL (skipped with fewer than two GPUs)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from oracle import tallax_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from tallax_b200 import sampling
+        from tests.conftest import to_dev
+
+        B, V = 64, 151936
+        x, tk, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=4, dtype="bf16")
+        vl = V // world
+        md = sampling.SamplingMetadata(top_k=to_dev(tk, dev), top_p=to_dev(tp, dev), temperature=to_dev(T, dev))
+        tok = sampling.sample_vocab_sharded(None, to_dev(x[:, rank * vl:(rank + 1) * vl], dev), md,
+                                            noise_shard=to_dev(noise[:, rank * vl:(rank + 1) * vl], dev), k_cand=50)
+        torch.cuda.synchronize()
+        q.put((rank, tok.cpu().numpy().tolist()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_sharded_two_gpus(cuda):
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    B, V = 64, 151936
+    x, tk, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=4, dtype="bf16")
+    exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
+    for r in range(world):
+        bad = (np.array(got[r]) != exp) & ~flags
+        assert not bad.any()
+    assert got[0] == got[1]
