@@ -41,11 +41,7 @@ namespace tlx {
 constexpr int kThreads = 256;        // slices kernel
 constexpr int kRowThreads = 512;     // merge kernel
 constexpr int kSliceBytes = 28672;   // one slice buffer (two per CTA)
-#ifdef TLX_CHUNK_BYTES
-constexpr int kChunkBytes = TLX_CHUNK_BYTES;
-#else
 constexpr int kChunkBytes = 4096;    // interleaving granule
-#endif
 constexpr int kChunksPerSlice = kSliceBytes / kChunkBytes;
 constexpr int kRecordCap = 2048;     // candidates (u64) a slice may publish == 16 KB payload
 constexpr int kMergeCap = 4096;      // candidates (u64) held in shared memory
@@ -59,6 +55,9 @@ enum RowClass : int { kGreedy = 0, kFast = 1, kGeneral = 2 };
 enum StatusBits : int { kStatusGeneral = 1, kStatusTimeout = 2, kStatusRedone = 4 };
 
 constexpr int kWarps = kThreads / 32;
+constexpr int kMaxWarps = 16;        // warps of the largest CTA that uses the per-warp result slots
+constexpr int kRowsKThreads = 256;   // rows kernel
+constexpr int kRowWarps = kRowsKThreads / 32;
 constexpr int kWarpCap = kRecordCap / kWarps;   // candidates one warp may publish per slice
 constexpr int kWarpHits = kSliceBytes / 16 / kWarps;   // vectors one warp owns in a slice
 static_assert(kWarps <= 16, "SliceHeader holds 16 per-warp counts");
@@ -77,10 +76,10 @@ static_assert(sizeof(SliceHeader) == 64, "SliceHeader layout");
 
 // What the warps of a CTA leave behind for the thread that publishes the slice.
 struct WarpResults {
-  unsigned long long top[kWarps];
-  unsigned short count[kWarps];
-  unsigned short bin[kWarps];
-  unsigned char overflow[kWarps];
+  unsigned long long top[kMaxWarps];
+  unsigned short count[kMaxWarps];
+  unsigned short bin[kMaxWarps];
+  unsigned char overflow[kMaxWarps];
   int cutoff_bin;
 };
 
@@ -117,6 +116,7 @@ struct SampleParams {
   int only_general;    // slices kernel: skip rows that the rows kernel finishes on its own
   int have_records;    // rows kernel: the slices kernel has written the records of the general rows
   int final_pass;      // slices kernel: score the kept elements of the general rows (third kernel)
+  int wide_elsewhere;  // rows kernel: the rows without top-k are sampled by the cluster kernel
   RowState* rowstate;
   unsigned long long div_magic;  // ceil(2^40 / S)
   // workspace
@@ -575,30 +575,35 @@ __device__ __forceinline__ void scan_tile(const unsigned char* buf, int elems, f
   const __nv_bfloat162 thr2 = __float2bfloat162_rn(thr);
   const uint4* vp = reinterpret_cast<const uint4*>(buf);
   int nhits = 0;
-  // step 1: per vector, a bit mask of the elements that are not (ordered and) below the threshold
-  auto vec_mask = [&](int i) -> uint32_t {
-    if (i >= nvec) return 0u;
-    const uint4 v = vp[i];
+  // step 1: per vector, a coarse test (may anything in it pass?) and, only where it says yes, a bit
+  // mask of the elements that are not (ordered and) below the threshold.  The coarse answers of a
+  // round are put to one warp vote, so that the usual round without any hit is a handful of
+  // instructions behind a warp-uniform branch.
+  auto coarse = [&](const uint4& v) -> bool {
     if constexpr (DT == TLX_BF16) {
       const __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(bf162_bits(v.x), bf162_bits(v.y)),
                                            __hmax2_nan(bf162_bits(v.z), bf162_bits(v.w)));
-      if (__hblt2(m, thr2)) return 0u;   // the common case: nothing in this vector
-      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-      uint32_t bits = 0;
+      return !__hblt2(m, thr2);
+    } else {
+      return !(__uint_as_float(v.x) < thr) || !(__uint_as_float(v.y) < thr) || !(__uint_as_float(v.z) < thr) ||
+             !(__uint_as_float(v.w) < thr);
+    }
+  };
+  auto fine = [&](const uint4& v) -> uint32_t {
+    const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+    uint32_t bits = 0;
+    if constexpr (DT == TLX_BF16) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint32_t below = __hlt2_mask(bf162_bits(w4[j]), thr2);   // 0xFFFF per half that is below
         bits |= ((below & 0xFFFFu) ? 0u : 1u) << (2 * j);
         bits |= ((below >> 16) ? 0u : 1u) << (2 * j + 1);
       }
-      return bits;
     } else {
-      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-      uint32_t bits = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) bits |= (__uint_as_float(w4[j]) < thr ? 0u : 1u) << j;
-      return bits;
     }
+    return bits;
   };
   // step 2: the noted elements, densely
   auto offer = [&](bool valid, int q) {
@@ -616,20 +621,39 @@ __device__ __forceinline__ void scan_tile(const unsigned char* buf, int elems, f
     __syncwarp();
     nhits = 0;
   };
-  for (int i0 = w * 32; i0 < nvec; i0 += blockDim.x) {
-    const int i = i0 + lane;
-    uint32_t bits = vec_mask(i);
-    while (__any_sync(0xFFFFFFFFu, bits != 0u)) {   // one element per lane and round
-      const bool have = bits != 0u;
-      const uint32_t mask = __ballot_sync(0xFFFFFFFFu, have);
-      if (have) {
-        const int t = __ffs(bits) - 1;
-        bits &= bits - 1;
-        hits[nhits + __popc(mask & lt_mask)] = (unsigned short)(i * VEC + t);
-      }
-      nhits += __popc(mask);
+  constexpr int kRound = 4;   // vectors per lane and round
+  for (int base = w * 32; base < nvec; base += kRound * (int)blockDim.x) {
+    uint4 v[kRound];
+    bool maybe[kRound];
+    bool any = false;
+#pragma unroll
+    for (int u = 0; u < kRound; ++u) {
+      const int i = base + u * (int)blockDim.x + lane;
+      v[u] = i < nvec ? vp[i] : make_uint4(0u, 0u, 0u, 0u);
     }
-    if (nhits > kHitCap - 32 * VEC) flush();   // room for one more round of vectors
+#pragma unroll
+    for (int u = 0; u < kRound; ++u) {
+      maybe[u] = (base + u * (int)blockDim.x + lane < nvec) && coarse(v[u]);
+      any |= maybe[u];
+    }
+    const bool go = __any_sync(0xFFFFFFFFu, any);
+    if (!go) continue;
+#pragma unroll
+    for (int u = 0; u < kRound; ++u) {
+      const int i = base + u * (int)blockDim.x + lane;
+      uint32_t bits = maybe[u] ? fine(v[u]) : 0u;
+      while (__any_sync(0xFFFFFFFFu, bits != 0u)) {   // one element per lane and turn
+        const bool have = bits != 0u;
+        const uint32_t mask = __ballot_sync(0xFFFFFFFFu, have);
+        if (have) {
+          const int t = __ffs(bits) - 1;
+          bits &= bits - 1;
+          hits[nhits + __popc(mask & lt_mask)] = (unsigned short)(i * VEC + t);
+        }
+        nhits += __popc(mask);
+      }
+      if (nhits > kHitCap - 32 * VEC) flush();   // room for one more vector per lane
+    }
   }
   flush();
   if (w == 0)   // ragged tail of the row's last tile (fewer than VEC elements)
@@ -637,30 +661,115 @@ __device__ __forceinline__ void scan_tile(const unsigned char* buf, int elems, f
 }
 
 // Appends every element of the tile at or above bin `bin` to the candidate list; `col_of(q)`
-// maps a local position to its column.
-template <int DT, typename ColOf>
+// maps a local position to its column.  Warp-local in two steps.  Step 1: every lane brings in
+// four vectors and puts one packed question to each (may anything in it pass?); the answers go
+// to a single warp vote, and the usual round, without any such vector, ends there.  Otherwise the
+// indices of those vectors are noted in the warp's list `hits`.  Step 2, once per tile: the
+// listed vectors are looked at densely, one element per lane.
+template <int DT, int WARPS, typename ColOf>
 __device__ __forceinline__ void collect_tile(const unsigned char* buf, int elems, int bin, SelectShared& s,
                                              uint64_t* cand, unsigned short* hits, ColOf col_of) {
-  const uint32_t lt_mask = (1u << lane_id()) - 1u;
-  scan_tile<DT>(buf, elems, bin_lower_value(bin), (uint32_t)bin << kHistShift, hits,
-                [&](bool pass, uint32_t key, int q) {
-                  const uint32_t mask = __ballot_sync(0xFFFFFFFFu, pass);
-                  if (mask) {
-                    int base = 0;
-                    if (lane_id() == __ffs(mask) - 1) base = atomicAdd(&s.fill, __popc(mask));
-                    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(mask) - 1);
-                    if (pass) {
-                      const int pos = base + __popc(mask & lt_mask);
-                      if (pos < kMergeCap) cand[pos] = cand_make(key, (uint32_t)col_of(q));
-                    }
-                  }
-                });
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  constexpr int kHitCap = kHistBins * 2 / WARPS;    // the idle histogram holds the warps' lists (u16 entries)
+  constexpr int kRound = 4;                         // vectors per lane and round
+  constexpr int kPerStep = 32 / VEC;                // listed vectors one step of the dense pass covers
+  const float thr = bin_lower_value(bin);
+  const uint32_t min_key = (uint32_t)bin << kHistShift;
+  const int nvec = elems / VEC;
+  const uint4* vp = reinterpret_cast<const uint4*>(buf);
+  const int lane = lane_id(), w = warp_id();
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  const __nv_bfloat162 thr2 = __float2bfloat162_rn(thr);
+  int noted = 0;
+  // Dense pass over listed positions, kSteps * 32 at a time: all loads first, then all votes, one
+  // reservation in the candidate list, then the stores, so that the steps' latencies overlap.
+  constexpr int kSteps = 4;
+  auto offer_batch = [&](const bool (&valid)[kSteps], const int (&q)[kSteps]) {
+    uint32_t key[kSteps], mask[kSteps];
+    int total = 0;
+#pragma unroll
+    for (int j = 0; j < kSteps; ++j) key[j] = valid[j] ? Elem<DT>::key(slice_elem<DT>(buf, q[j])) : 0u;
+#pragma unroll
+    for (int j = 0; j < kSteps; ++j) {
+      mask[j] = __ballot_sync(0xFFFFFFFFu, valid[j] && key[j] >= min_key);
+      total += __popc(mask[j]);
+    }
+    if (total == 0) return;
+    int run = 0;
+    if (lane == 0) run = atomicAdd(&s.fill, total);
+    run = __shfl_sync(0xFFFFFFFFu, run, 0);
+#pragma unroll
+    for (int j = 0; j < kSteps; ++j) {
+      if (mask[j] & (1u << lane)) {
+        const int pos = run + __popc(mask[j] & lt_mask);
+        if (pos < kMergeCap) cand[pos] = cand_make(key[j], (uint32_t)col_of(q[j]));
+      }
+      run += __popc(mask[j]);
+    }
+  };
+  auto flush = [&]() {
+    __syncwarp();
+    for (int k = 0; k < noted; k += kSteps * kPerStep) {
+      bool valid[kSteps];
+      int q[kSteps];
+#pragma unroll
+      for (int j = 0; j < kSteps; ++j) {
+        const int slot = k + j * kPerStep + lane / VEC;
+        valid[j] = slot < noted;
+        q[j] = valid[j] ? (int)hits[slot] * VEC + (lane % VEC) : 0;
+      }
+      offer_batch(valid, q);
+    }
+    __syncwarp();
+    noted = 0;
+  };
+  for (int base = w * 32; base < nvec; base += kRound * (int)blockDim.x) {
+    uint4 v[kRound];
+    bool maybe[kRound];
+    bool any = false;
+#pragma unroll
+    for (int u = 0; u < kRound; ++u) {
+      const int i = base + u * (int)blockDim.x + lane;
+      v[u] = i < nvec ? vp[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < kRound; ++u) {
+      const bool inside = base + u * (int)blockDim.x + lane < nvec;
+      if constexpr (DT == TLX_BF16) {
+        const __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(bf162_bits(v[u].x), bf162_bits(v[u].y)),
+                                             __hmax2_nan(bf162_bits(v[u].z), bf162_bits(v[u].w)));
+        maybe[u] = inside && !__hblt2(m, thr2);
+      } else {
+        maybe[u] = inside && (!(__uint_as_float(v[u].x) < thr) || !(__uint_as_float(v[u].y) < thr) ||
+                              !(__uint_as_float(v[u].z) < thr) || !(__uint_as_float(v[u].w) < thr));
+      }
+      any |= maybe[u];
+    }
+    const bool go = __any_sync(0xFFFFFFFFu, any);
+    if (!go) continue;
+#pragma unroll
+    for (int u = 0; u < kRound; ++u) {
+      const uint32_t mask = __ballot_sync(0xFFFFFFFFu, maybe[u]);
+      if (maybe[u]) hits[noted + __popc(mask & lt_mask)] = (unsigned short)(base + u * (int)blockDim.x + lane);
+      noted += __popc(mask);
+    }
+    if (noted > kHitCap - kRound * 32) flush();
+  }
+  flush();
+  if (w == 0 && nvec * VEC < elems) {   // ragged end of the row's last tile (fewer than VEC elements)
+    bool valid[kSteps];
+    int q[kSteps];
+#pragma unroll
+    for (int j = 0; j < kSteps; ++j) { valid[j] = j == 0 && nvec * VEC + lane < elems; q[j] = nvec * VEC + lane; }
+    offer_batch(valid, q);
+  }
 }
 
 // Raises the threshold bin to the largest one that still has K candidates at or above it and
 // drops the candidates below it.  The histogram is rebuilt from the list (it is not kept up
 // to date while collecting).  All threads call.
-__device__ __forceinline__ void refine_candidates(SelectShared& s, uint64_t* cand, int K) {
+static __device__ __noinline__ void refine_candidates(SelectShared& s, uint64_t* cand, int K) {
   for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) s.hist[i] = 0;
   __syncthreads();
   const int m = s.fill < kMergeCap ? s.fill : kMergeCap;
@@ -747,7 +856,7 @@ __device__ __forceinline__ void reduce_slice_final_bf16(const SampleParams& p, c
 template <typename T>
 __device__ __forceinline__ T ld_cg(const T* p) { return __ldcg(p); }
 
-__device__ __forceinline__ int merge_row_greedy(const SampleParams& p, int64_t row, SelectShared& s) {
+static __device__ __noinline__ int merge_row_greedy(const SampleParams& p, int64_t row, SelectShared& s) {
   uint64_t best = 0;
   if ((int)threadIdx.x < p.S) best = ld_cg(&record_header(p, row, threadIdx.x)->top);
   block_max_u64(best, s);
@@ -758,7 +867,7 @@ __device__ __forceinline__ int merge_row_greedy(const SampleParams& p, int64_t r
 // into cand[]; returns their number, or -1 if the published sets cannot be trusted to hold
 // the row's top-K (a segment overflowed, or fewer than K candidates).  A row's candidates
 // sit in S * kWarps segments (one per slice and publishing warp).
-__device__ __forceinline__ int gather_candidates(const SampleParams& p, int64_t row, int K, SelectShared& s,
+static __device__ __noinline__ int gather_candidates(const SampleParams& p, int64_t row, int K, SelectShared& s,
                                                  uint64_t* cand) {
   if (threadIdx.x == 0) { s.tmp_i[0] = 0; s.tmp_i[1] = 0; s.fill = 0; }
   __syncthreads();
@@ -803,19 +912,20 @@ __device__ __forceinline__ int gather_candidates(const SampleParams& p, int64_t 
   return (m > kMergeCap || m < K) ? -1 : m;
 }
 
+// Number of the `n` listed tokens below `tok`.
+static __device__ __noinline__ uint32_t tie_rank(const uint32_t* tie_tok, int n, uint32_t tok) {
+  uint32_t rank = 0;
+  for (int j = 0; j < n; ++j) rank += tie_tok[j] < tok ? 1u : 0u;
+  return rank;
+}
+
 // Sampler tail on unsorted bf16 candidates, without sorting them: a histogram over the
 // candidates' 16-bit keys gives the top-k boundary (key and admitted ties), the softmax
 // denominator and the top-p threshold exactly as in the whole-row path (the mass of a value
 // group is count * exp(value - max)); the Gumbel arg-max then runs over the kept candidates.
 // Needs the keys to span at most kHistBins values; returns -1 otherwise (caller sorts).
-__device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row, int K, float pp, float T_, int m,
+static __device__ __noinline__ int tail_bf16_hist(const SampleParams& p, int64_t row, int K, float pp, float T_, int m,
                                               SelectShared& s, const uint64_t* cand) {
-#ifdef TLX_PROFILE
-  long long tq0 = clock64(), tq1; long long qa[8]; int qi = 0;
-#define TLX_Q { tq1 = clock64(); qa[qi++] = tq1 - tq0; tq0 = tq1; }
-#else
-#define TLX_Q
-#endif
   uint32_t kmx = 0, kmn = 0xFFFFFFFFu;
   for (int i = threadIdx.x; i < m; i += blockDim.x) {
     const uint32_t k16 = cand_key(cand[i]) >> 16;
@@ -831,7 +941,6 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
   __syncthreads();
   for (int i = threadIdx.x; i < m; i += blockDim.x) atomicAdd(&win[kmax - (int)(cand_key(cand[i]) >> 16)], 1u);
   __syncthreads();
-  TLX_Q
   const float xmax = key16_value(kmax);
   const int per = (W + (int)blockDim.x - 1) / (int)blockDim.x;
   const int i0 = threadIdx.x * per;
@@ -853,8 +962,6 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
   __syncthreads();
   const int vk_idx = s.tmp_i[0];
   const uint32_t ties_admitted = (uint32_t)s.tmp_i[1], ties_total = (uint32_t)s.tmp_i[2];
-
-  TLX_Q
   // denominator and top-p threshold over the top-k set
   double mass = 0.0;
   for (int j = 0; j < per; ++j) {
@@ -886,8 +993,6 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
   const int vstar_idx = s.tmp_i[3];
   const bool cut_ties = vstar_idx == vk_idx && ties_admitted < ties_total;
   __syncthreads();
-
-  TLX_Q
   // the lowest tokens of the boundary group are the admitted ones: list the group's tokens
   uint32_t* tie_tok = s.hist;   // the histogram is no longer needed
   if (cut_ties) {
@@ -900,8 +1005,6 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
     __syncthreads();
   }
   const int n_ties = cut_ties ? s.fill : 0;
-
-  TLX_Q
   // Gumbel arg-max over the kept candidates, screened in f32 (see final_argmax)
   const int64_t nrow = row + p.dim0_offset;
   float a1 = -INFINITY, a2 = -INFINITY, q1 = 0.f, u1 = 0.5f;
@@ -910,40 +1013,44 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
     const int idx = kmax - (int)(cand_key(c) >> 16);
     if (idx > vstar_idx) return false;
     if (idx < vk_idx || !cut_ties) return true;
-    uint32_t rank = 0;   // idx == vk_idx: admitted if fewer than ties_admitted group members have a lower token
-    const uint32_t tok = cand_low(c);
-    for (int j = 0; j < n_ties; ++j) rank += tie_tok[j] < tok ? 1u : 0u;
-    return rank < ties_admitted;
+    // idx == vk_idx: admitted if fewer than ties_admitted group members have a lower token
+    return tie_rank(tie_tok, n_ties, cand_low(c)) < ties_admitted;
   };
   {
-    // first decide which of the thread's candidates are kept and start all their noise loads
-    constexpr int kPerMax = kMergeCap / kThreads;   // the smaller of the two kernels' block sizes bounds it
-    uint32_t keep_mask = 0;
-    float uu[kPerMax];
+    // decide which of the thread's candidates are kept and start their noise loads, four at a time
+    constexpr int kBatch = 4;
+#pragma unroll 1
+    for (int i0b = threadIdx.x; i0b < m; i0b += kBatch * (int)blockDim.x) {
+      uint32_t keep_mask = 0;
+      float uu[kBatch];
+      uint64_t cc[kBatch];
 #pragma unroll
-    for (int j = 0; j < kPerMax; ++j) {
-      const int i = threadIdx.x + j * blockDim.x;
-      uu[j] = 0.5f;
-      if (i < m) {
-        const uint64_t c = cand[i];
-        if (kept(c)) { keep_mask |= 1u << j; uu[j] = p.noise.at(nrow, (int64_t)cand_low(c)); }
+      for (int j = 0; j < kBatch; ++j) {
+        const int i = i0b + j * (int)blockDim.x;
+        uu[j] = 0.5f;
+        cc[j] = 0;
+        if (i < m) {
+          cc[j] = cand[i];
+          if (kept(cc[j])) { keep_mask |= 1u << j; uu[j] = p.noise.at(nrow, (int64_t)cand_low(cc[j])); }
+        }
       }
-    }
 #pragma unroll
-    for (int j = 0; j < kPerMax; ++j) {
-      if (keep_mask & (1u << j)) {
-        const uint64_t c = cand[threadIdx.x + j * blockDim.x];
-        const float q = __fdiv_rn(key_f32(cand_key(c)), T_);
-        const float a = q + gumbel_fast(uu[j]);
-        if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = uu[j]; c1 = (int)cand_low(c); }
-        else if (a > a2) a2 = a;
+      for (int j = 0; j < kBatch; ++j) {
+        if (keep_mask & (1u << j)) {
+          const float q = __fdiv_rn(key_f32(cand_key(cc[j])), T_);
+          const float a = q + gumbel_screen(uu[j]);
+          if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = uu[j]; c1 = (int)cand_low(cc[j]); }
+          else if (a > a2) a2 = a;
+        }
       }
     }
   }
-  TLX_Q
   const Best top = block_best(Best{a1, c1}, s);
   const float cut = top.y - (kGumbelSlack + 1e-5f * fabsf(top.y));
+  const int leaders = __syncthreads_count(a1 >= cut);
   const int crowded = __syncthreads_or(a2 >= cut);
+  // nothing else comes within the slack of the best screened score: it is the winner as it stands
+  if (leaders == 1 && !crowded) return top.tok;
   Best best{-INFINITY, 0x7FFFFFFF};
   if (!crowded) {
     if (a1 >= cut) best = Best{q1 + gumbel_exact(u1), c1};
@@ -953,22 +1060,16 @@ __device__ __forceinline__ int tail_bf16_hist(const SampleParams& p, int64_t row
       if (kept(c)) {
         const float u = p.noise.at(nrow, (int64_t)cand_low(c));
         const float q = __fdiv_rn(key_f32(cand_key(c)), T_);
-        if (q + gumbel_fast(u) >= cut) best = best_of(best, Best{q + gumbel_exact(u), (int)cand_low(c)});
+        if (q + gumbel_screen(u) >= cut) best = best_of(best, Best{q + gumbel_exact(u), (int)cand_low(c)});
       }
     }
   }
-  TLX_Q
   const int result = block_best(best, s).tok;
-#ifdef TLX_PROFILE
-  TLX_Q
-  if (threadIdx.x == 0 && (blockIdx.x % 61) == 0)
-    printf("tail m %d W %d ties %d cut %d crowded %d | hist %lld boundary %lld mass %lld tielist %lld screen %lld decide %lld best %lld\n", m, W, n_ties, (int)cut_ties, crowded, qa[0], qa[1], qa[2], qa[3], qa[4], qa[5], qa[6]);
-#endif
   return result;
 }
 
 template <int DT>
-__device__ __forceinline__ int merge_row_fast(const SampleParams& p, int64_t row, int K, float pp, float T_,
+static __device__ __noinline__ int merge_row_fast(const SampleParams& p, int64_t row, int K, float pp, float T_,
                                               SelectShared& s, uint64_t* cand, int* status) {
   using T = typename Elem<DT>::type;
   const T* rowp = reinterpret_cast<const T*>(p.logits) + row * p.row_stride;
@@ -992,7 +1093,7 @@ __device__ __forceinline__ int merge_row_fast(const SampleParams& p, int64_t row
       [&](int i) { return p.noise.at(nrow, (int64_t)cand_low(cand[i])); });
 }
 
-__device__ __forceinline__ int merge_row_general_bf16(const SampleParams& p, int64_t row, int K, float pp, float T_,
+static __device__ __noinline__ int merge_row_general_bf16(const SampleParams& p, int64_t row, int K, float pp, float T_,
                                                       SelectShared& s, uint32_t* win, bool threshold_only = false) {
   const __nv_bfloat16* rowp = reinterpret_cast<const __nv_bfloat16*>(p.logits) + row * p.row_stride;
   if (threadIdx.x == 0) s.tmp_i[0] = 0;
@@ -1060,10 +1161,6 @@ __device__ __forceinline__ int merge_row_general_bf16(const SampleParams& p, int
   return general_row_bf16<kWin>(rowp, p.vocab, K, pp, T_, p.noise, row + p.dim0_offset, s, win, pre);
 }
 
-// ---- the kernels --------------------------------------------------------------------------
-constexpr size_t kSlicesSmem = kSharedHeader + kUnionBytes + 2 * (size_t)kSliceBytes + sizeof(Control);
-constexpr size_t kMergeSmem = kSharedHeader + kUnionBytes;
-
 // class and effective top-k of a row, from global memory
 __device__ __forceinline__ int classify_row(const SampleParams& p, int64_t row, int& K) {
   K = p.top_k[row];
@@ -1071,6 +1168,14 @@ __device__ __forceinline__ int classify_row(const SampleParams& p, int64_t row, 
   if (p.temperature[row] < kSamplingEps) return (int)kGreedy;
   return K <= kFastK ? (int)kFast : (int)kGeneral;
 }
+
+}  // namespace tlx
+#include "sampler_wide.cuh"
+namespace tlx {
+
+// ---- the kernels --------------------------------------------------------------------------
+constexpr size_t kSlicesSmem = kSharedHeader + kUnionBytes + 2 * (size_t)kSliceBytes + sizeof(Control);
+constexpr size_t kMergeSmem = kSharedHeader + kUnionBytes;
 
 // Kernel 1: persistent CTAs stream the slices (statically assigned: CTA c takes the items
 // c, c + grid, ...) and write one record per slice.  Nothing in the per-slice path waits on
@@ -1266,7 +1371,7 @@ __global__ void __launch_bounds__(kRowThreads) sample_merge_kernel(SampleParams 
 constexpr size_t kRowsSmem = kSharedHeader + kUnionBytes + 2 * (size_t)kSliceBytes + sizeof(Control);
 
 template <int DT>
-__global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p) {
+__global__ void __launch_bounds__(kRowsKThreads, 2) sample_rows_kernel(SampleParams p) {
   using T = typename Elem<DT>::type;
   constexpr int VEC = 16 / (int)sizeof(T);
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -1278,7 +1383,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p
   uint32_t* win = reinterpret_cast<uint32_t*>(uni);
   double* massbins = reinterpret_cast<double*>(uni);
   // while a row is collected its histogram area is idle and holds the warps' hit lists
-  unsigned short* hits = reinterpret_cast<unsigned short*>(s.hist) + warp_id() * (kHistBins * 2 / kWarps);
+  unsigned short* hits = reinterpret_cast<unsigned short*>(s.hist) + warp_id() * (kHistBins * 2 / kRowWarps);
 
   // The tiles of a row are its S interleaved slices: every tile is a sample of the whole row,
   // so the threshold estimated on the first one is already right for the others.
@@ -1304,6 +1409,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p
     const float pp = p.top_p[row], T_ = p.temperature[row];
     int status = 0, tok = 0;
     // rows without top-k only get their threshold here: the final pass is the third kernel's
+    if (DT == TLX_BF16 && p.wide_elsewhere && cls == kGeneral && (int64_t)K >= n) continue;   // the cluster kernel's
     const bool deferred = DT == TLX_BF16 && cls == kGeneral && (int64_t)K >= n && p.have_records;
     if (!deferred) {
       load(0, 0);
@@ -1345,8 +1451,12 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p
         }
       }
     } else {
-      if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
       unsigned long long wbest = 0;   // greedy: this warp's running arg-max (key << 32 | 0x7FFFFFFF - column)
+      // A first threshold that turns out too high (fewer than K candidates at the end of the row)
+      // costs one more pass over the row with a lower one, then a second, then the exact select.
+      int forced_bin = -1;
+      for (int attempt = 0;; ++attempt) {
+      if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
       __syncthreads();
       for (int t = 0; t < p.S; ++t) {
         const int b = t & 1;
@@ -1365,7 +1475,10 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p
             }
           }
         } else {
-          if (t == 0) {
+          if (t == 0 && forced_bin >= 0) {
+            if (threadIdx.x == 0) s.bin = forced_bin;
+            __syncthreads();
+          } else if (t == 0) {
             // First threshold, from the maxima of the threads' elements: aim at 1.3 K + 32 elements of
             // the ROW, i.e. that fraction of this tile.  Too high an estimate is caught at the end
             // (fewer than K candidates), too low a one by the refinement below.
@@ -1377,13 +1490,16 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p
             const uint32_t tkey = thread_max_key<DT>(buf, nvec, vecs);
             const int my_bin = ((int)threadIdx.x < nvec) ? (int)(tkey >> kHistShift) : -1;
             const int holders = nvec < (int)blockDim.x ? nvec : (int)blockDim.x;
-            int want = (int)((float)holders * (1.f - __expf(-(float)(vecs * VEC) * frac)) + 0.999f);
-            want = want < 1 ? 1 : want;
+            // one standard deviation of the count of holders above the wanted threshold as margin
+            float wantf = (float)holders * (1.f - __expf(-(float)(vecs * VEC) * frac));
+            wantf += sqrtf(wantf);
+            int want = (int)(wantf + 0.999f);
+            want = want < 1 ? 1 : (want > holders ? holders : want);
             const int b0 = (frac >= 0.5f || nvec == 0) ? 0 : vote_threshold_bin(my_bin, want);
             if (threadIdx.x == 0) s.bin = b0;
             __syncthreads();
           }
-          collect_tile<DT>(buf, elems, s.bin, s, cand, hits, [&](int q) { return g.column(t, q); });
+          collect_tile<DT, kRowWarps>(buf, elems, s.bin, s, cand, hits, [&](int q) { return g.column(t, q); });
         }
         __syncthreads();   // the tile is consumed, its buffer is free
         load(t + 2, b);
@@ -1393,12 +1509,22 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p
             (s.fill > kMergeCap / 2 || (t == p.S - 1 && DT != TLX_BF16 && s.fill > 2 * K + 64)))
           refine_candidates(s, cand, K);
       }
+      if (cls == kGreedy) break;
+      const int m_try = s.fill, bin_try = s.bin;
+      __syncthreads();
+      if (m_try >= K || bin_try == 0 || attempt == 2) break;
+      forced_bin = bin_try - (attempt == 0 ? 1 : 4);
+      forced_bin = forced_bin < 0 ? 0 : forced_bin;
+      status |= kStatusRedone;
+      load(0, 0);
+      load(1, 1);
+      }
       if (cls == kGreedy) {
         unsigned long long* slot = reinterpret_cast<unsigned long long*>(s.scan_f64);
         if (lane_id() == 0) slot[warp_id()] = wbest;
         __syncthreads();
         unsigned long long best = 0;
-        for (int w = 0; w < kWarps; ++w) best = slot[w] > best ? slot[w] : best;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) best = slot[w] > best ? slot[w] : best;
         tok = 0x7FFFFFFF - (int32_t)(uint32_t)best;
         __syncthreads();
       } else {
@@ -1411,7 +1537,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_rows_kernel(SampleParams p
           __syncthreads();
         }
         tok = -1;
-        if constexpr (DT == TLX_BF16) tok = tail_bf16_hist(p, row, K, pp, T_, m, s, cand);
+        if constexpr (DT == TLX_BF16) if (tok < 0) tok = tail_bf16_hist(p, row, K, pp, T_, m, s, cand);
         if (tok < 0) {
           __syncthreads();
           sort_candidates(cand, m);
@@ -1567,7 +1693,7 @@ __global__ void __launch_bounds__(256) gumbel_argmax_kernel(const float* __restr
     const float f = threefry_uniform01(k0, k1, (uint32_t)((int64_t)idx0[e] * dim1 + (int64_t)idx1[e]));
     const float u = fmaxf(f, kF32Tiny);
     const float l = logits[e];
-    const float a = l + gumbel_fast(u);
+    const float a = l + gumbel_screen(u);
     if (a >= best.y - (kGumbelSlack + 1e-5f * fabsf(best.y)) || best.y == -INFINITY)
       best = best_of(best, Best{l + gumbel_exact(u), (int)i});
   }
@@ -1596,6 +1722,32 @@ static int ensure_smem(const void* func, size_t bytes, const char* what) {
   if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "%s: cudaFuncSetAttribute(%zu): %s", what, bytes, cudaGetErrorString(e));
   if (used < 256) cache[used++] = Entry{func, dev, bytes};
   return TLX_OK;
+}
+
+// A helper stream with the two events that fork it from and join it to the caller's stream.
+// One per host thread and device, made on first use and kept for the life of the process.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+static SideStream* side_stream() {
+  static thread_local SideStream cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  SideStream& ss = cache[dev];
+  if (!ss.stream) {
+    cudaStream_t st = nullptr;
+    cudaEvent_t a = nullptr, b = nullptr;
+    if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;   // the caller falls back to its own stream
+    }
+    ss.stream = st; ss.fork = a; ss.join = b;
+  }
+  return &ss;
 }
 
 static int device_sm_count() {
@@ -1673,16 +1825,45 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
   p.rowstate = reinterpret_cast<RowState*>((unsigned char*)workspace + 256);
   p.records = (unsigned char*)workspace + counters_bytes(rows);
 
-  cudaError_t e = cudaMemsetAsync(workspace, 0, 256, st);
-  if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaMemsetAsync: %s", cudaGetErrorString(e));
   const int64_t items = rows * l.S;
   const int64_t slots = 2ll * device_sm_count();
+  const int64_t wide_vecs_per_cta = ((vocab >> 3) + kWideCluster - 1) / kWideCluster;
+  const bool resident_wide = 2 * rows >= slots && dtype == TLX_BF16 && p.use_tma && wide_vecs_per_cta * 16 <= kWidePartBytes;
+  if (!resident_wide) {   // the flags in the workspace are only used by the slices kernel and its merges
+    cudaError_t e = cudaMemsetAsync(workspace, 0, 256, st);
+    if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  }
   int rc;
   if (2 * rows >= slots) {
     // at least half a row per CTA slot: one CTA per row; only the rows whose top-k is disabled or
     // large are cut into slices first (their histograms need every SM), by the slices kernel
     const unsigned grid = (unsigned)(rows < slots ? rows : slots);
-    if (dtype == TLX_BF16) {
+    if (resident_wide) {
+      // rows without top-k: one cluster per row, the row resident in the cluster's shared memory
+      if ((rc = ensure_smem((const void*)sample_wide_rows_kernel, kWideSmem, "sample")) != TLX_OK) return rc;
+      if ((rc = ensure_smem((const void*)sample_rows_kernel<TLX_BF16>, kRowsSmem, "sample")) != TLX_OK) return rc;
+      int64_t clusters = slots / kWideCluster;
+      clusters = clusters < 1 ? 1 : (clusters > rows ? rows : clusters);
+      // The two kernels work on disjoint rows: the cluster kernel goes to a side stream forked
+      // from the caller's stream and joined back to it, so that they share the GPU.
+      SideStream* side = side_stream();
+      cudaStream_t wst = st;
+      if (side && cudaEventRecord(side->fork, st) == cudaSuccess &&
+          cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
+        wst = side->stream;
+      sample_wide_rows_kernel<<<(unsigned)(clusters * kWideCluster), kThreads, kWideSmem, wst>>>(p);
+      TLX_CHECK_LAUNCH("sample (wide rows)");
+      if (wst != st) {
+        cudaError_t je = cudaEventRecord(side->join, wst);
+        if (je != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaEventRecord: %s", cudaGetErrorString(je));
+      }
+      p.wide_elsewhere = 1;
+      sample_rows_kernel<TLX_BF16><<<grid, kRowsKThreads, kRowsSmem, st>>>(p);
+      if (wst != st) {
+        cudaError_t je = cudaStreamWaitEvent(st, side->join, 0);
+        if (je != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaStreamWaitEvent: %s", cudaGetErrorString(je));
+      }
+    } else if (dtype == TLX_BF16) {
       p.only_general = 1;
       p.have_records = 1;
       const unsigned sgrid = (unsigned)(items < slots ? items : slots);
@@ -1690,13 +1871,13 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
       if ((rc = ensure_smem((const void*)sample_rows_kernel<TLX_BF16>, kRowsSmem, "sample")) != TLX_OK) return rc;
       sample_slices_kernel<TLX_BF16><<<sgrid, kThreads, kSlicesSmem, st>>>(p);
       TLX_CHECK_LAUNCH("sample (slices)");
-      sample_rows_kernel<TLX_BF16><<<grid, kThreads, kRowsSmem, st>>>(p);
+      sample_rows_kernel<TLX_BF16><<<grid, kRowsKThreads, kRowsSmem, st>>>(p);
       TLX_CHECK_LAUNCH("sample (rows)");
       p.final_pass = 1;   // rows without top-k: Gumbel arg-max over the kept elements, slice by slice
       sample_slices_kernel<TLX_BF16><<<sgrid, kThreads, kSlicesSmem, st>>>(p);
     } else {
       if ((rc = ensure_smem((const void*)sample_rows_kernel<TLX_F32>, kRowsSmem, "sample")) != TLX_OK) return rc;
-      sample_rows_kernel<TLX_F32><<<grid, kThreads, kRowsSmem, st>>>(p);
+      sample_rows_kernel<TLX_F32><<<grid, kRowsKThreads, kRowsSmem, st>>>(p);
     }
     TLX_CHECK_LAUNCH("sample (rows)");
     return TLX_OK;

@@ -33,7 +33,7 @@ __device__ __forceinline__ void block_max_u64(uint64_t& v, SelectShared& s) {
 
 // (max key, lowest column holding it) of a row, as key << 32 | (0x7FFFFFFF - column).
 template <int DT>
-__device__ __forceinline__ uint64_t row_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n,
+static __device__ __noinline__ uint64_t row_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n,
                                                SelectShared& s) {
   using T = typename Elem<DT>::type;
   uint64_t best = 0;
@@ -51,7 +51,7 @@ __device__ __forceinline__ uint64_t row_argmax(const typename Elem<DT>::type* __
 // Softmax denominator over the top-k set by streaming: sum of exp(x - xmax) over keys
 // > vk (all keys when !bounded); the caller adds the admitted ties.
 template <int DT>
-__device__ __forceinline__ double stream_mass(const typename Elem<DT>::type* __restrict__ row, int64_t n, float xmax,
+static __device__ __noinline__ double stream_mass(const typename Elem<DT>::type* __restrict__ row, int64_t n, float xmax,
                                               bool bounded, uint32_t vk, SelectShared& s) {
   using T = typename Elem<DT>::type;
   // compensated f32 sum per thread (the exp itself is f32), f64 across threads
@@ -119,7 +119,7 @@ __device__ __forceinline__ Best block_best(Best best, SelectShared& s) {
 }
 
 template <int DT>
-__device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n, float T_,
+static __device__ __noinline__ int final_argmax(const typename Elem<DT>::type* __restrict__ row, int64_t n, float T_,
                                             uint32_t vstar, bool bounded, uint32_t vk, uint32_t ties_admitted,
                                             bool ordered, const NoiseSrc& noise, int64_t nrow, SelectShared& s) {
   // screening pass: two best screened scores per thread, with what is needed to re-evaluate the best
@@ -128,7 +128,7 @@ __device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __res
   for_each_kept<DT>(row, n, vstar, bounded, vk, ties_admitted, ordered, s, [&](float x, int64_t c) {
     const float u = noise.at(nrow, c);
     const float q = __fdiv_rn(x, T_);
-    const float a = q + gumbel_fast(u);
+    const float a = q + gumbel_screen(u);
     if (a > a1) { a2 = a1; a1 = a; q1 = q; u1 = u; c1 = (int)c; }
     else if (a > a2) a2 = a;
   });
@@ -142,7 +142,7 @@ __device__ __forceinline__ int final_argmax(const typename Elem<DT>::type* __res
     for_each_kept<DT>(row, n, vstar, bounded, vk, ties_admitted, ordered, s, [&](float x, int64_t c) {
       const float u = noise.at(nrow, c);
       const float q = __fdiv_rn(x, T_);
-      if (q + gumbel_fast(u) >= cut) best = best_of(best, Best{q + gumbel_exact(u), (int)c});
+      if (q + gumbel_screen(u) >= cut) best = best_of(best, Best{q + gumbel_exact(u), (int)c});
     });
   }
   return block_best(best, s).tok;
@@ -157,7 +157,7 @@ __device__ __forceinline__ float key16_value(int k16) { return key_f32(key16_to_
 
 // Histogram of the keys in [whi - WIN + 1, whi] into win[whi - key16].
 template <int WIN>
-__device__ __forceinline__ void window_hist(const __nv_bfloat16* __restrict__ row, int64_t n, int whi, uint32_t* win) {
+static __device__ __noinline__ void window_hist(const __nv_bfloat16* __restrict__ row, int64_t n, int whi, uint32_t* win) {
   for (int i = threadIdx.x; i < WIN; i += blockDim.x) win[i] = 0;
   __syncthreads();
   for_each_elem<TLX_BF16>(row, 0, n, [&](__nv_bfloat16 v, int64_t) {
@@ -178,7 +178,7 @@ struct RowPreset {
 
 // One row, any top-k.  `win` holds WIN uint32 bins; blockDim.x must divide WIN.
 template <int WIN>
-__device__ __forceinline__ int general_row_bf16(const __nv_bfloat16* __restrict__ row, int64_t n, int K, float p_row,
+static __device__ __noinline__ int general_row_bf16(const __nv_bfloat16* __restrict__ row, int64_t n, int K, float p_row,
                                                 float T_, const NoiseSrc& noise, int64_t nrow, SelectShared& s,
                                                 uint32_t* win, const RowPreset& pre) {
   const int kPer = WIN / (int)blockDim.x;  // window slots per thread, descending key order
@@ -287,7 +287,7 @@ __device__ __forceinline__ int general_row_bf16(const __nv_bfloat16* __restrict_
 // ---- any float dtype: 32-bit keys, radix digits of 12 / 12 / 8 bits -----------------------
 // `mass` holds kHistBins doubles; blockDim.x must divide kHistBins.
 template <int DT>
-__device__ __forceinline__ int general_row_radix(const typename Elem<DT>::type* __restrict__ row, int64_t n, int K,
+static __device__ __noinline__ int general_row_radix(const typename Elem<DT>::type* __restrict__ row, int64_t n, int K,
                                                  float p_row, float T_, const NoiseSrc& noise, int64_t nrow,
                                                  SelectShared& s, double* mass) {
   using T = typename Elem<DT>::type;

@@ -97,7 +97,7 @@ __device__ __forceinline__ float elem_as_float(typename Elem<DT>::type v) {
 // ---- threshold refinement -------------------------------------------------------
 // Largest bin B with (#elements in bins >= B) >= K, from the histogram; 0 if fewer
 // than K elements were counted.  Also returns the count in bins > B.  All threads call.
-__device__ __forceinline__ void find_threshold_bin(SelectShared& s, int K, int lower_bound_bin) {
+static __device__ __noinline__ void find_threshold_bin(SelectShared& s, int K, int lower_bound_bin) {
   const int nt = blockDim.x;
   const int per = kHistBins / nt;  // blockDim divides 4096
   // thread t owns the bins [hi - per + 1, hi], hi = 4095 - t*per (descending order)
@@ -126,7 +126,7 @@ __device__ __forceinline__ void find_threshold_bin(SelectShared& s, int K, int l
 // Drop candidates whose bin fell below s.bin.  In place: every thread first reads its
 // contiguous share, then (after the scan's barriers) writes the survivors.
 template <int CAP>
-__device__ __forceinline__ void compact_candidates(SelectShared& s, uint64_t* cand) {
+static __device__ __noinline__ void compact_candidates(SelectShared& s, uint64_t* cand) {
   constexpr int kMaxPer = 16;
   const int n = min(s.fill, CAP);
   const int per = (n + blockDim.x - 1) / blockDim.x;  // <= CAP / blockDim <= kMaxPer
@@ -245,7 +245,7 @@ __device__ __forceinline__ bool collect_row(const typename Elem<DT>::type* __res
 // lowest-indexed ties.  Digits of 12, 12 and 8 bits; 3 counting passes + 2 passes for
 // the ordered collection.  Slow, but independent of the data's order or tie structure.
 template <int DT>
-__device__ __forceinline__ void exact_select_row(const typename Elem<DT>::type* __restrict__ row, int64_t n, int K,
+static __device__ __noinline__ void exact_select_row(const typename Elem<DT>::type* __restrict__ row, int64_t n, int K,
                                                  SelectShared& s, uint64_t* cand) {
   using T = typename Elem<DT>::type;
   uint32_t prefix = 0, prefix_mask = 0;
@@ -297,7 +297,7 @@ __device__ __forceinline__ void exact_select_row(const typename Elem<DT>::type* 
 }
 
 // Pads cand[m .. P) with the greatest composite and sorts; returns P (power of two >= m).
-__device__ __forceinline__ int sort_candidates(uint64_t* cand, int m) {
+static __device__ __noinline__ int sort_candidates(uint64_t* cand, int m) {
   int P = 2;
   while (P < m) P <<= 1;
   for (int i = m + threadIdx.x; i < P; i += blockDim.x) cand[i] = ~0ull;
@@ -315,7 +315,7 @@ __device__ __forceinline__ int sort_candidates(uint64_t* cand, int m) {
 // contenders only.  K <= kMaxItems * blockDim.x.  All threads call; the result is valid
 // in every thread.
 template <int kMaxItems, typename ValueOf, typename TokenOf, typename NoiseOf>
-__device__ __forceinline__ int sample_tail(int K, float p, float T, SelectShared& s, ValueOf value_of,
+static __device__ __noinline__ int sample_tail(int K, float p, float T, SelectShared& s, ValueOf value_of,
                                            TokenOf token_of, NoiseOf noise_of) {
   const int per = (K + blockDim.x - 1) / blockDim.x;
   const int i0 = threadIdx.x * per;
@@ -355,7 +355,7 @@ __device__ __forceinline__ int sample_tail(int K, float p, float T, SelectShared
     a[j] = -INFINITY;
     if (j < per && i < K && x[j] >= thr) {
       u[j] = noise_of(i);
-      a[j] = __fdiv_rn(x[j], T) + gumbel_fast(u[j]);
+      a[j] = __fdiv_rn(x[j], T) + gumbel_screen(u[j]);
       amax = fmaxf(amax, a[j]);
     }
   }

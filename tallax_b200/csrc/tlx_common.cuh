@@ -193,9 +193,16 @@ __device__ __forceinline__ float threefry_uniform01(uint32_t k0, uint32_t k1, ui
   return __uint_as_float((bits >> 9) | 0x3F800000u) - 1.0f;
 }
 
+// Out-of-line copy for the samplers, which read noise at many places: the twenty rounds inlined
+// at each of them made their kernels outgrow the instruction cache.
+static __device__ __noinline__ float threefry_uniform01_call(uint32_t k0, uint32_t k1, uint32_t counter_lo) {
+  return threefry_uniform01(k0, k1, counter_lo);
+}
+
 // ---- Gumbel noise ---------------------------------------------------------------
 // Exact form: evaluated in f64, rounded to f32 once (bit-identical to the CPU checker).
-__device__ __forceinline__ float gumbel_exact(float u) {
+// Out of line on purpose (two f64 logarithms, used at many places, on few elements).
+static __device__ __noinline__ float gumbel_exact(float u) {
   double d = (double)fmaxf(u, kF32Tiny);
   return (float)(-log(-log(d)));
 }
@@ -205,10 +212,11 @@ __device__ __forceinline__ float gumbel_fast(float u) {
 }
 // Cheapest screening form: hardware log2 for both logs.  -log(u) loses relative accuracy as u -> 1,
 // so the last percent takes the accurate log1p; elsewhere the absolute error stays below 5e-5.
+static __device__ __noinline__ float neg_log_near_one(float u) { return -log1pf(u - 1.0f); }
 __device__ __forceinline__ float gumbel_screen(float u) {
   u = fmaxf(u, kF32Tiny);
   float l = -__logf(u);
-  if (u > 0.99f) l = -log1pf(u - 1.0f);
+  if (u > 0.99f) l = neg_log_near_one(u);
   return -__logf(l);
 }
 constexpr float kGumbelSlack = 1e-3f;
@@ -221,7 +229,7 @@ struct NoiseSrc {
   int64_t vocab;          // counter = row * vocab + token
   __device__ __forceinline__ float at(int64_t row, int64_t tok) const {
     if (dense) return __ldg(dense + row * stride + tok);
-    float f = threefry_uniform01(k0, k1, (uint32_t)(row * vocab + tok));
+    float f = threefry_uniform01_call(k0, k1, (uint32_t)(row * vocab + tok));
     return fmaxf(f, kF32Tiny);
   }
 };
