@@ -186,23 +186,45 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    lib = _lib.load()
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
+    # One CUDA graph per input set, each holding one sampler call: a timed step is one graph launch, so
+    # that the host's launch path (Python, ctypes, several driver calls per step) is not what is measured.
+    graphs, launches_per_call = [], 0
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for j in range(N_SETS):
+                g = torch.cuda.CUDAGraph()
+                before = lib.tlx_kernel_launches()
+                with torch.cuda.graph(g, stream=side):
+                    step(j)
+                launches_per_call = lib.tlx_kernel_launches() - before
+                graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        for j in range(N_SETS):
+            graphs[j].replay()
+    barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    lib = _lib.load()
     with ClockSampler(local_rank) as clocks:
         time.sleep(0.15)
         barrier()
         launches0 = lib.tlx_kernel_launches()
         start.record()
         for i in range(args.steps):
-            step(i)
+            if graphs:
+                graphs[i % N_SETS].replay()
+            else:
+                step(i)
         stop.record()
-        launches = lib.tlx_kernel_launches() - launches0
+        launches = (launches_per_call * args.steps) if graphs else (lib.tlx_kernel_launches() - launches0)
         barrier()
         time.sleep(0.1)
     ms = start.elapsed_time(stop)
+    rank_ms = ms
 
     # ---- end to end through the public API from pinned host buffers --------------------------
     h_logits = torch.empty((B, V), dtype=torch.bfloat16).pin_memory()
@@ -238,7 +260,11 @@ def run_ours(args):
     e2e_ms = e0.elapsed_time(e1)
 
     times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    per_rank = [rank_ms]
     if world > 1:
+        gathered = [torch.zeros(1, dtype=torch.float64, device=device) for _ in range(world)]
+        dist.all_gather(gathered, times[:1].clone())
+        per_rank = [float(t.item()) for t in gathered]
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = times.tolist()
 
@@ -264,6 +290,8 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "batch_per_gpu": B, "vocab": V, "sharding": f"batch rows x{world}",
                        "l2": f"{N_SETS} rotating input sets ({N_SETS * B * V * 2 / 1e6:.0f} MB of logits > 126 MB L2)"},
             "clocks": clocks.summary(),
+            "ms_per_step_by_rank": [t / args.steps for t in per_rank],
+            "launch": "one CUDA graph launch per step" if graphs else "one library call per step",
             "e2e": {"value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
                     "h2d_bytes_per_step": B * V * 2 + B * V * 4 + B * 12, "d2h_bytes_per_step": B * 4,
                     "ms_per_step": e2e_ms / e2e_steps},
@@ -290,6 +318,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="time plain library calls instead of CUDA graph launches")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

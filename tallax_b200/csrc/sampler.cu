@@ -8,14 +8,19 @@
 //
 // tlx_sample, batches with at least one row per two CTA slots (the decode case):
 //   rows kernel    one CTA per row.  Greedy rows keep a running arg-max.  Rows with
-//                  1 <= top_k <= kFastK estimate a threshold bin on their first slice, append
-//                  what lies at or above it to a candidate list in shared memory (one packed
-//                  compare per two elements; the bin is raised exactly, from a histogram of the
-//                  list, when the list fills up) and finish inside the CTA: top-k boundary,
-//                  softmax mass and top-p threshold from a histogram over the candidates' keys
-//                  (bf16; sorted candidates for f32), Gumbel arg-max over the kept ones.
-//   rows whose top-k is disabled (bf16) need per-value counts of the whole row, which only
-//   pays off with every SM helping, so they take three steps:
+//                  1 <= top_k <= kFastK estimate a threshold bin on their first slice and note, per
+//                  warp, the vectors that hold something at or above it (one packed compare per
+//                  vector, one warp vote per four vectors a lane); the noted vectors are looked at
+//                  densely once per slice and their passing elements appended to a candidate list
+//                  in shared memory (the bin is raised exactly, from a histogram of the list, when
+//                  the list fills up).  The row finishes inside the CTA: top-k boundary, softmax
+//                  mass and top-p threshold from a histogram over the candidates' keys (bf16;
+//                  sorted candidates for f32), Gumbel arg-max over the kept ones.
+//   cluster kernel (sampler_wide.cuh, bf16 rows whose top-k is disabled) one cluster of eight CTAs
+//                  per row keeps the row resident in shared memory; it runs on a side stream
+//                  next to the rows kernel, since the two work on disjoint rows.
+//   When the cluster kernel does not apply (rows not 16-byte aligned, vocabulary too long for the
+//   cluster's shared memory) those rows take three steps instead:
 //     slices kernel   (before the rows kernel) per slice: maximum, histogram of the 2048 16-bit
 //                     keys below it, sum of exp(x - max) of everything lower;
 //     rows kernel     adds the slices' histograms up, takes the top-p threshold from them (the
@@ -29,9 +34,11 @@
 // and merged per row by the merge kernel, so that every SM streams whatever the batch size.
 //
 // Nothing on a per-slice path waits for a global-memory round trip (while the bulk copies
-// saturate the memory system such a round trip costs microseconds), results are exact: a
-// threshold estimate that turns out too high is detected (fewer than top_k candidates) and
-// the row is redone by the exact multi-pass select.
+// saturate the memory system such a round trip costs microseconds).  Results are exact: a
+// threshold estimate that turns out too high is detected (fewer than top_k candidates) and the
+// row is streamed again with a lower one; the exact multi-pass select is the last resort.
+// Routines that run once per row or less are kept out of line, which keeps the per-slice loops
+// small in the instruction cache.
 #include <mutex>
 
 #include "sampler_general.cuh"

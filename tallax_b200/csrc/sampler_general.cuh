@@ -167,6 +167,19 @@ static __device__ __noinline__ void window_hist(const __nv_bfloat16* __restrict_
   __syncthreads();
 }
 
+// Largest 16-bit key of the row that is <= `limit`, or -1 (also when limit < 0).  All threads call.
+static __device__ __noinline__ int next_key_below(const __nv_bfloat16* __restrict__ row, int64_t n, int limit,
+                                                  SelectShared& s) {
+  if (limit < 0) return -1;
+  uint64_t best = 0;   // key + 1, 0 = none
+  for_each_elem<TLX_BF16>(row, 0, n, [&](__nv_bfloat16 v, int64_t) {
+    const int k16 = (int)(Elem<TLX_BF16>::key(v) >> 16);
+    if (k16 <= limit && (uint64_t)(k16 + 1) > best) best = (uint64_t)(k16 + 1);
+  });
+  block_max_u64(best, s);
+  return (int)best - 1;
+}
+
 // What a caller may already know about the row (the sliced sampler assembles these from
 // its slices); anything absent is computed from global memory.
 struct RowPreset {
@@ -244,7 +257,7 @@ static __device__ __noinline__ int general_row_bf16(const __nv_bfloat16* __restr
   {
     double cum = 0.0;
     const int lowest = bounded ? vk16 : 0;
-    for (int whi = kmax; whi >= lowest; whi -= WIN) {
+    for (int whi = kmax; whi >= lowest;) {
       if (hist_whi != whi) { window_hist<WIN>(row, n, whi, win); hist_whi = whi; }
       const int i0 = threadIdx.x * kPer;
       double local = 0.0;
@@ -276,6 +289,9 @@ static __device__ __noinline__ int general_row_bf16(const __nv_bfloat16* __restr
       __syncthreads();
       if (found >= 0) { vstar16 = found; break; }
       cum += total;
+      // the next window hangs from the largest key present below this one (the keys in between,
+      // e.g. the denormal range between the positive and the negative values, are skipped)
+      whi = next_key_below(row, n, whi - WIN, s);
     }
   }
   if (pre.threshold_only && !bounded) return vstar16;

@@ -37,13 +37,47 @@ struct __align__(16) WideExchange {   // what the CTAs of a cluster read from on
 
 struct __align__(16) WideControl {
   unsigned long long mbar;
-  double z;
+  double z, zb;
   int timeout;
   int list[kThreads];
 };
 
 constexpr size_t kWideSmem = kSharedHeader + (size_t)kWin * 4 + sizeof(WideExchange) + sizeof(WideControl) + 128 +
                              (size_t)kWidePartBytes;
+
+// First key (descending) of the window [whi - kWin + 1, whi] at which `cum` plus the running mass
+// count * exp(value - xmax) reaches `target`, or -1 if the window ends before that.  All threads call.
+static __device__ __noinline__ int window_threshold(const uint32_t* win, int whi, float xmax, double target, double cum,
+                                                    SelectShared& s) {
+  const int per = kWin / (int)blockDim.x;
+  const int i0 = (int)threadIdx.x * per;
+  double local = 0.0;
+  for (int j = 0; j < per; ++j) {
+    const int k16 = whi - (i0 + j);
+    const uint32_t c = win[i0 + j];
+    if (c && k16 >= 0) local += (double)c * (double)expf(key16_value(k16) - xmax);
+  }
+  double total;
+  const double incl = block_scan_incl<double>(local, s.scan_f64, &total, ShflUpF64());
+  const double before = cum + incl - local;
+  if (threadIdx.x == 0) s.tmp_i[3] = -1;
+  __syncthreads();
+  if (before < target && before + local >= target) {
+    double run = before;
+    for (int j = 0; j < per; ++j) {
+      const int k16 = whi - (i0 + j);
+      const uint32_t c = win[i0 + j];
+      if (c && k16 >= 0) {
+        run += (double)c * (double)expf(key16_value(k16) - xmax);
+        if (run >= target) { s.tmp_i[3] = k16; break; }
+      }
+    }
+  }
+  __syncthreads();
+  const int found = s.tmp_i[3];
+  __syncthreads();
+  return found;
+}
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -137,80 +171,116 @@ __global__ void __cluster_dims__(kWideCluster, 1, 1) __launch_bounds__(kThreads,
       const float xmax = key_f32(kmax32);
 
       // ---- 2./3. threshold (top_p >= 1 keeps the whole row) -------------------------------
+      // The threshold is looked for window by window: first the kWin keys below the row maximum,
+      // then, if the cumulative mass has not reached top_p * Z there, the kWin keys below the
+      // largest key that is present under that window, and so on.  Every further window costs two
+      // more passes over the resident share, none over global memory.
       int vstar16 = 0;
       if (pp < 1.0f) {
-        for (int i = threadIdx.x; i < kWin; i += blockDim.x) win[i] = 0;
-        __syncthreads();
         const float neg_xmax_l2e = -xmax * 1.44269504f;
-        float below = 0.f;
-        if (kmax >= 0x8000 + kWin) {
-          // positive maximum (the usual case): every negative element is below the window, and one
-          // unsigned compare of (kmax - 0x8000) - h against the window size decides for the others
-          const uint32_t dpos = (uint32_t)(kmax - 0x8000);
-          auto visit = [&](uint32_t h, float x) {
-            const uint32_t d = dpos - h;
-            if (d < (uint32_t)kWin) atomicAdd(&win[d], 1u);
-            else below += ex2_approx(fmaf(x, 1.44269504f, neg_xmax_l2e));
-          };
-          for (int i = threadIdx.x; i < myvec; i += blockDim.x) {
-            const uint4 v = vp[i];
-            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+        int whi = kmax;
+        double cum = 0.0, target = 0.0;
+        for (int round = 0;; ++round) {
+          for (int i = threadIdx.x; i < kWin; i += blockDim.x) win[i] = 0;
+          __syncthreads();
+          float below = 0.f;
+          if (round == 0 && kmax >= 0x8000 + kWin) {
+            // positive maximum (the usual case): every negative element is below the window, and one
+            // unsigned compare of (kmax - 0x8000) - h against the window size decides for the others
+            const uint32_t dpos = (uint32_t)(kmax - 0x8000);
+            auto visit = [&](uint32_t h, float x) {
+              const uint32_t d = dpos - h;
+              if (d < (uint32_t)kWin) atomicAdd(&win[d], 1u);
+              else below += ex2_approx(fmaf(x, 1.44269504f, neg_xmax_l2e));
+            };
+            for (int i = threadIdx.x; i < myvec; i += blockDim.x) {
+              const uint4 v = vp[i];
+              const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              visit(w4[q] & 0xFFFFu, __uint_as_float(w4[q] << 16));
-              visit(w4[q] >> 16, __uint_as_float(w4[q] & 0xFFFF0000u));
+              for (int q = 0; q < 4; ++q) {
+                visit(w4[q] & 0xFFFFu, __uint_as_float(w4[q] << 16));
+                visit(w4[q] >> 16, __uint_as_float(w4[q] & 0xFFFF0000u));
+              }
+            }
+          } else {
+            auto visit = [&](uint32_t h) {
+              const uint32_t k16 = (h & 0x8000u) ? (~h & 0xFFFFu) : (h | 0x8000u);
+              const int d = whi - (int)k16;
+              if (d < kWin) { if (d >= 0) atomicAdd(&win[d], 1u); }
+              else if (round == 0) below += ex2_approx(fmaf(__uint_as_float(h << 16), 1.44269504f, neg_xmax_l2e));
+            };
+            for (int i = threadIdx.x; i < myvec; i += blockDim.x) {
+              const uint4 v = vp[i];
+              const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) { visit(w4[q] & 0xFFFFu); visit(w4[q] >> 16); }
             }
           }
-        } else {
-          auto visit = [&](uint32_t h) {
-            const uint32_t k16 = (h & 0x8000u) ? (~h & 0xFFFFu) : (h | 0x8000u);
-            const int d = kmax - (int)k16;
-            if (d < kWin) { if (d >= 0) atomicAdd(&win[d], 1u); }
-            else below += ex2_approx(fmaf(__uint_as_float(h << 16), 1.44269504f, neg_xmax_l2e));
-          };
+          if (round == 0) {
+            double below_cta;
+            block_scan_incl<double>((double)below, s.scan_f64, &below_cta, ShflUpF64());
+            if (threadIdx.x == 0) xch.below = below_cta;
+          }
+          cluster.sync();
+          // this CTA's eighth of the bins, summed over the cluster, and its mass
+          {
+            const int bin = rank * kWideBinsPer + (int)threadIdx.x;
+            uint32_t c = 0;
+#pragma unroll
+            for (int q = 0; q < kWideCluster; ++q) c += cluster.map_shared_rank(win, q)[bin];
+            xch.combined[threadIdx.x] = c;
+            const double m = (c && whi - bin >= 0) ? (double)c * (double)expf(key16_value(whi - bin) - xmax) : 0.0;
+            double mass_cta;
+            block_scan_incl<double>(m, s.scan_f64, &mass_cta, ShflUpF64());
+            if (threadIdx.x == 0) xch.mass = mass_cta;
+          }
+          cluster.sync();
+          // every CTA assembles the window's histogram and mass (and, the first time, the denominator)
+#pragma unroll
+          for (int q = 0; q < kWideCluster; ++q)
+            win[q * kWideBinsPer + threadIdx.x] = cluster.map_shared_rank(&xch, q)->combined[threadIdx.x];
+          if (threadIdx.x == 0) {
+            double zw = 0.0, zb = 0.0;
+            for (int q = 0; q < kWideCluster; ++q) {
+              const WideExchange* o = cluster.map_shared_rank(&xch, q);
+              zw += o->mass;
+              zb += o->below;
+            }
+            ctl.z = zw;
+            ctl.zb = zb;
+          }
+          __syncthreads();
+          const double wmass = ctl.z;
+          if (round == 0) target = (double)pp * (wmass + ctl.zb);
+          const int found = window_threshold(win, whi, xmax, target, cum, s);
+          if (found >= 0) { vstar16 = found; break; }
+          cum += wmass;
+          // the next window hangs from the largest key that is present below this one
+          const int lo = whi - kWin;
+          if (lo < 0) break;
+          uint32_t next = 0;   // key + 1, 0 = nothing below
           for (int i = threadIdx.x; i < myvec; i += blockDim.x) {
             const uint4 v = vp[i];
             const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { visit(w4[q] & 0xFFFFu); visit(w4[q] >> 16); }
+            for (int q = 0; q < 8; ++q) {
+              const uint32_t h = (q & 1) ? (w4[q >> 1] >> 16) : (w4[q >> 1] & 0xFFFFu);
+              const uint32_t k16 = (h & 0x8000u) ? (~h & 0xFFFFu) : (h | 0x8000u);
+              if ((int)k16 <= lo && k16 + 1 > next) next = k16 + 1;
+            }
           }
-        }
-        double below_cta;
-        block_scan_incl<double>((double)below, s.scan_f64, &below_cta, ShflUpF64());
-        if (threadIdx.x == 0) xch.below = below_cta;
-        cluster.sync();
-        // this CTA's eighth of the bins, summed over the cluster, and its mass
-        {
-          const int b = rank * kWideBinsPer + (int)threadIdx.x;
-          uint32_t c = 0;
+          next = block_max_u32(next, s.scan_u32);
+          if (threadIdx.x == 0) xch.kmax32 = next;
+          cluster.sync();
+          next = 0;
 #pragma unroll
-          for (int q = 0; q < kWideCluster; ++q) c += cluster.map_shared_rank(win, q)[b];
-          xch.combined[threadIdx.x] = c;
-          const double m = (c && kmax - b >= 0) ? (double)c * (double)expf(key16_value(kmax - b) - xmax) : 0.0;
-          double mass_cta;
-          block_scan_incl<double>(m, s.scan_f64, &mass_cta, ShflUpF64());
-          if (threadIdx.x == 0) xch.mass = mass_cta;
-        }
-        cluster.sync();
-        // every CTA assembles the row's histogram and denominator
-#pragma unroll
-        for (int q = 0; q < kWideCluster; ++q)
-          win[q * kWideBinsPer + threadIdx.x] = cluster.map_shared_rank(&xch, q)->combined[threadIdx.x];
-        if (threadIdx.x == 0) {
-          double z = 0.0;
           for (int q = 0; q < kWideCluster; ++q) {
-            const WideExchange* o = cluster.map_shared_rank(&xch, q);
-            z += o->mass + o->below;
+            const uint32_t k = cluster.map_shared_rank(&xch, q)->kmax32;
+            next = k > next ? k : next;
           }
-          ctl.z = z;
+          if (next == 0) break;   // nothing left: the whole row is kept
+          whi = (int)next - 1;
         }
-        __syncthreads();
-        RowPreset pre;
-        pre.top = ((uint64_t)key16_to_key32((uint32_t)kmax) << 32) | 1ull;
-        pre.have_window = true;
-        pre.mass = ctl.z;
-        pre.threshold_only = true;
-        vstar16 = general_row_bf16<kWin>(rowp, n, (int)n, pp, T_, p.noise, nrow, s, win, pre);
       }
 
       // ---- 4. Gumbel arg-max over the kept elements of the share ---------------------------

@@ -90,6 +90,32 @@ def test_sample_general_path_cases(cuda, dtype):
     assert (status[[0, 1, 2, 3]] & 1).all()
 
 
+def test_sample_rows_without_top_k_in_a_large_batch(cuda):
+    # Large batches send the rows without top-k to the cluster kernel (the row resident in shared
+    # memory).  Flat rows push the top-p boundary below the first histogram window, into the
+    # negative values, so the window-by-window search is exercised, next to ties, masks and top_p = 1.
+    B, V = 320, 32768
+    rng = np.random.default_rng(5)
+    x, tk, tp, T, noise = o.make_sampling_inputs(B=B, V=V, seed=31, dtype="bf16")
+    tk[:] = rng.integers(1, 600, B)
+    wide = np.arange(B) % 2 == 0
+    tk[wide] = 0
+    scale = np.where(np.arange(B) % 4 == 0, 0.05, 1.0).astype(np.float32)[:, None]   # every other wide row is flat
+    x = (x.astype(np.float32) * scale).astype(o.bfloat16)
+    tp[:] = rng.uniform(0.3, 0.98, B).astype(np.float32)
+    tp[8] = 1.0
+    tp[12] = 0.9999
+    x[16] = (np.arange(V) % 5).astype(np.float32).astype(o.bfloat16)        # five value groups
+    x[20] = (-np.abs(x[20].astype(np.float32)) - 1.0).astype(o.bfloat16)    # all negative
+    x[24, 50:] = -np.inf                                                    # almost everything masked
+    x[28] = 0.0                                                             # a single value group
+    exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
+    got, status = _run(cuda, x, tk, tp, T, noise=noise)
+    _assert_tokens(got, exp, flags, min_checked=0.8)
+    assert (status[wide] & 1).all() and (status & 2 == 0).all()
+    assert (~flags[(np.arange(B) % 4 == 0)]).mean() > 0.5   # the flat rows are really checked
+
+
 def test_sample_fast_path_overflow_falls_back(cuda):
     # ascending rows overflow the candidate list; the general kernel must answer them
     V = 70000
