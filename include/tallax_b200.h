@@ -167,8 +167,12 @@ int tlx_top_p_and_sample(void* stream, const void* topk_logits, int dtype, const
  * logits [rows, vocab] (F32 or BF16, row stride in elements) -> token ids int32[rows]
  * in one call: per-row top-k (0 or >= vocab disables it), top-p, temperature,
  * Gumbel noise (dense tensor or threefry key as above), greedy override.
- * out_status (nullable, device int32[rows]): bit 0 = general path used, bit 1 = a bounded
- * wait gave up (result invalid).
+ * out_status (nullable, device int32[rows]): bit 0 = the row took a path for rows without
+ * (or with a very large) top-k, bit 1 = a bounded wait gave up (result invalid), bit 2 = the
+ * row needed a second pass (first threshold too high, or candidate list overflow).
+ * For large bf16 batches part of the work runs on a stream owned by the library, forked from
+ * `stream` and joined back to it inside the call: all of the call's work is ordered on `stream`
+ * as seen by the caller.
  * Replaces the whole of tallax/_src/sampling.py:331-343 (`sample`), i.e. the
  * top_dynamic_k kernel (top_k.py:482-506) followed by _top_p_and_sample.            */
 size_t tlx_sample_workspace_bytes(int64_t rows, int64_t vocab);
