@@ -312,6 +312,71 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_op_workload(args):
+    """Rows/s and roofline fraction of the other operators at their benchmark sizes (one GPU)."""
+    import torch
+    from tallax_b200 import _lib, tax, tumpy
+    _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev)
+    w = args.workload
+    if w == "c1":      # exact top-k, f32 [8, 32768], k = 64
+        rows, n = 8, 32768
+        g.manual_seed(0)
+        xs = [torch.randn((rows, n), generator=g, device=dev) for _ in range(4)]
+        fn = lambda i: tax.top_k(xs[i % 4], 64)
+        algo, note = rows * n * 4 + rows * 64 * 8, "read keys once + write k values and indices"
+    elif w == "c2":    # stable ascending sort with payload, f32 [128, 65536]
+        rows, n = 128, 65536
+        g.manual_seed(1)
+        ks = [torch.randn((rows, n), generator=g, device=dev) for _ in range(3)]
+        pay = torch.arange(n, dtype=torch.int32, device=dev).repeat(rows, 1)
+        fn = lambda i: tax.sort([ks[i % 3], pay], num_keys=1, is_stable=True)
+        algo, note = 2 * rows * n * 8, "one read + one write of keys and payload (the op is compare-exchange-bound)"
+    elif w in ("c4a", "c4a-single-pass"):   # top-k, f32 [1024, 262144], k = 128
+        rows, n = 1024, 262144
+        g.manual_seed(3)
+        x = torch.randn((rows, n), generator=g, device=dev)   # 1 GiB > L2
+        from tallax_b200._src import ops
+        fn = (lambda i: tax.top_k(x, 128)) if w == "c4a" else (lambda i: ops.top_k(x, 128, single_pass=True))
+        algo, note = rows * n * 4 + rows * 128 * 8, "read keys once + write k values and indices"
+    elif w == "c4b":   # gather, i32 indices [1024, 4096] into f32 [1024, 262144]
+        rows, n = 1024, 262144
+        g.manual_seed(3)
+        x = torch.randn((rows, n), generator=g, device=dev)
+        ind = torch.randint(0, n, (rows, 4096), generator=g, device=dev, dtype=torch.int32)
+        fn = lambda i: tumpy.take_along_axis(x, ind, axis=1)
+        algo, note = 3 * rows * 4096 * 4, "indices + gathered elements + output (32-byte sectors: 134 217 728 B)"
+    else:
+        raise SystemExit(f"unknown workload {w}")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+    for i in range(max(args.warmup, 3)):
+        fn(i)
+    torch.cuda.synchronize()
+    total = 0.0
+    with ClockSampler(0) as clocks:
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(i)
+            e1.record()
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+    ms = total / args.steps
+    peak, peak_src = peaks()
+    achieved = algo / (ms / 1e3) / 1e9
+    print(json.dumps({
+        "metric": "rows_per_s", "value": rows / (ms / 1e3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w, "rows": rows, "row_length": n, "l2": "256 MB flush buffer written between steps"},
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src, "note": note}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -319,7 +384,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="time plain library calls instead of CUDA graph launches")
+    ap.add_argument("--workload", default="c3", help="c3 (default, the fused sampler) | c1 | c2 | c4a | "
+                    "c4a-single-pass | c4b: the other operators at their benchmark sizes, one GPU, rows/s")
     args = ap.parse_args()
+    if args.workload != "c3" and args.impl == "ours":
+        run_op_workload(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
