@@ -1508,13 +1508,20 @@ __global__ void __launch_bounds__(kRowsKThreads, 2) sample_rows_kernel(SamplePar
           }
           collect_tile<DT, kRowWarps>(buf, elems, s.bin, s, cand, hits, [&](int q) { return g.column(t, q); });
         }
-        __syncthreads();   // the tile is consumed, its buffer is free
+        // The tile is consumed, its buffer is free.  The same barrier carries the decision to raise the
+        // threshold, which is due when the candidate list fills up (and once at the end for the sorting
+        // tail, which wants few candidates).  It must be the same for every thread (the refinement has
+        // barriers of its own), but a thread that read the fill level after the barrier could see what
+        // a faster warp has already appended from the next tile: so every thread reads it before, and
+        // the block takes the OR.
+        const int fill_seen = s.fill;
+        const int refine_now = __syncthreads_or(
+            cls == kFast && (fill_seen > kMergeCap / 2 || (t == p.S - 1 && DT != TLX_BF16 && fill_seen > 2 * K + 64)));
         load(t + 2, b);
-        // The threshold only has to rise when the candidate list fills up (and once at the end for
-        // the sorting tail, which wants few candidates).
-        if (cls == kFast && s.fill <= kMergeCap &&
-            (s.fill > kMergeCap / 2 || (t == p.S - 1 && DT != TLX_BF16 && s.fill > 2 * K + 64)))
-          refine_candidates(s, cand, K);
+        if (refine_now) {
+          __syncthreads();   // nobody is ahead in the next tile while the fill level is looked at again
+          if (s.fill <= kMergeCap) refine_candidates(s, cand, K);
+        }
       }
       if (cls == kGreedy) break;
       const int m_try = s.fill, bin_try = s.bin;
