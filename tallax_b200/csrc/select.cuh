@@ -49,12 +49,11 @@ __device__ __forceinline__ float bin_lower_value(int b) {
 // ---- vectorised row traversal ---------------------------------------------------
 // Calls f(value, column) for every column in [c0, c1), 16-byte loads in the aligned
 // body, kU vectors in flight per thread.
-template <int DT, typename F>
+template <int DT, int kU = 4, typename F>
 __device__ __forceinline__ void for_each_elem(const typename Elem<DT>::type* __restrict__ row, int64_t c0, int64_t c1,
                                               F&& f) {
   using T = typename Elem<DT>::type;
   constexpr int VEC = 16 / (int)sizeof(T);
-  constexpr int kU = 4;
   if (c1 <= c0) return;
   const uintptr_t addr = reinterpret_cast<uintptr_t>(row + c0);
   int64_t head = (int64_t)(((16 - (addr & 15)) & 15) / sizeof(T));
@@ -211,7 +210,7 @@ __device__ __forceinline__ bool collect_row(const typename Elem<DT>::type* __res
     __syncthreads();
     const int bin = s.bin;
     if constexpr (DT == TLX_I32 || DT == TLX_U32) {
-      for_each_elem<DT>(row, done, upto, [&](T v, int64_t c) {
+      for_each_elem<DT, 8>(row, done, upto, [&](T v, int64_t c) {
         const uint32_t key = Elem<DT>::key(v);
         if ((int)(key >> kHistShift) >= bin) {
           atomicAdd(&s.hist[key >> kHistShift], 1u);
@@ -220,7 +219,7 @@ __device__ __forceinline__ bool collect_row(const typename Elem<DT>::type* __res
       });
     } else {
       const float thr = bin_lower_value(bin);
-      for_each_elem<DT>(row, done, upto, [&](T v, int64_t c) {
+      for_each_elem<DT, 8>(row, done, upto, [&](T v, int64_t c) {
         if (!(elem_as_float<DT>(v) < thr)) {
           const uint32_t key = Elem<DT>::key(v);
           if ((int)(key >> kHistShift) >= bin) {
