@@ -6,8 +6,9 @@
 //      maximum; the cluster agrees on the row maximum through distributed shared memory;
 //   2. every CTA histograms its share over the window of 16-bit keys below the row maximum and
 //      sums exp(x - max) of what lies below the window;
-//   3. the CTAs add the histograms up (each one an eighth of the bins), every CTA then holds the
-//      row's histogram and denominator and finds the top-p threshold from counts * exp(value);
+//   3. the CTAs add the histograms up (each one an eighth of the bins) and look, each in its
+//      eighth, for the bin at which the cumulative mass count * exp(value - max) reaches
+//      top_p times the denominator: the top-p threshold;
 //   4. every CTA takes the Gumbel arg-max over the kept elements of its share (noise read with
 //      coalesced 16-byte loads), decides its winner on the f64-evaluated Gumbel term, and rank 0
 //      picks the best of the winners.
@@ -31,53 +32,17 @@ struct __align__(16) WideExchange {   // what the CTAs of a cluster read from on
   float top_a;                        // best screened score of this CTA's share and its token
   int top_tok;
   int leaders;                        // contenders in this CTA's share (2 = more than can be told apart)
-  int pad;
-  uint32_t combined[kWideBinsPer];
+  uint32_t found;                     // key + 1 of the threshold bin if it lies in this CTA's share of the bins
 };
 
 struct __align__(16) WideControl {
   unsigned long long mbar;
-  double z, zb;
   int timeout;
   int list[kThreads];
 };
 
 constexpr size_t kWideSmem = kSharedHeader + (size_t)kWin * 4 + sizeof(WideExchange) + sizeof(WideControl) + 128 +
                              (size_t)kWidePartBytes;
-
-// First key (descending) of the window [whi - kWin + 1, whi] at which `cum` plus the running mass
-// count * exp(value - xmax) reaches `target`, or -1 if the window ends before that.  All threads call.
-static __device__ __noinline__ int window_threshold(const uint32_t* win, int whi, float xmax, double target, double cum,
-                                                    SelectShared& s) {
-  const int per = kWin / (int)blockDim.x;
-  const int i0 = (int)threadIdx.x * per;
-  double local = 0.0;
-  for (int j = 0; j < per; ++j) {
-    const int k16 = whi - (i0 + j);
-    const uint32_t c = win[i0 + j];
-    if (c && k16 >= 0) local += (double)c * (double)expf(key16_value(k16) - xmax);
-  }
-  double total;
-  const double incl = block_scan_incl<double>(local, s.scan_f64, &total, ShflUpF64());
-  const double before = cum + incl - local;
-  if (threadIdx.x == 0) s.tmp_i[3] = -1;
-  __syncthreads();
-  if (before < target && before + local >= target) {
-    double run = before;
-    for (int j = 0; j < per; ++j) {
-      const int k16 = whi - (i0 + j);
-      const uint32_t c = win[i0 + j];
-      if (c && k16 >= 0) {
-        run += (double)c * (double)expf(key16_value(k16) - xmax);
-        if (run >= target) { s.tmp_i[3] = k16; break; }
-      }
-    }
-  }
-  __syncthreads();
-  const int found = s.tmp_i[3];
-  __syncthreads();
-  return found;
-}
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -222,39 +187,47 @@ __global__ void __cluster_dims__(kWideCluster, 1, 1) __launch_bounds__(kThreads,
             if (threadIdx.x == 0) xch.below = below_cta;
           }
           cluster.sync();
-          // this CTA's eighth of the bins, summed over the cluster, and its mass
+          // This CTA's eighth of the bins, summed over the cluster, and the running mass inside it.
+          // The search for the bin at which the cumulative mass reaches the target is distributed
+          // the same way: bin t of CTA r covers the interval (B_r + incl[t-1], B_r + incl[t]], with
+          // B_0 = cum and B_{r+1} = B_r + mass_r evaluated in this order by everybody, so that the
+          // intervals tile the line exactly and at most one bin claims the target.
+          double* incl_of = reinterpret_cast<double*>(win);   // once everybody has read it, this CTA's histogram may go
           {
             const int bin = rank * kWideBinsPer + (int)threadIdx.x;
             uint32_t c = 0;
 #pragma unroll
             for (int q = 0; q < kWideCluster; ++q) c += cluster.map_shared_rank(win, q)[bin];
-            xch.combined[threadIdx.x] = c;
             const double m = (c && whi - bin >= 0) ? (double)c * (double)expf(key16_value(whi - bin) - xmax) : 0.0;
             double mass_cta;
-            block_scan_incl<double>(m, s.scan_f64, &mass_cta, ShflUpF64());
-            if (threadIdx.x == 0) xch.mass = mass_cta;
-          }
-          cluster.sync();
-          // every CTA assembles the window's histogram and mass (and, the first time, the denominator)
+            const double incl = block_scan_incl<double>(m, s.scan_f64, &mass_cta, ShflUpF64());
+            if (threadIdx.x == 0) { xch.mass = mass_cta; xch.found = 0; }
+            cluster.sync();   // everybody has read everybody's histogram, the masses are out
+            incl_of[threadIdx.x] = incl;
+            double b_r = cum, b_all = cum, zb = 0.0;
 #pragma unroll
-          for (int q = 0; q < kWideCluster; ++q)
-            win[q * kWideBinsPer + threadIdx.x] = cluster.map_shared_rank(&xch, q)->combined[threadIdx.x];
-          if (threadIdx.x == 0) {
-            double zw = 0.0, zb = 0.0;
             for (int q = 0; q < kWideCluster; ++q) {
               const WideExchange* o = cluster.map_shared_rank(&xch, q);
-              zw += o->mass;
+              if (q == rank) b_r = b_all;
+              b_all += o->mass;
               zb += o->below;
             }
-            ctl.z = zw;
-            ctl.zb = zb;
+            if (round == 0) target = (double)pp * ((b_all - cum) + zb);
+            __syncthreads();
+            const double lo_m = b_r + (threadIdx.x ? incl_of[threadIdx.x - 1] : 0.0);
+            const double hi_m = b_r + incl;
+            if (m > 0.0 && lo_m < target && hi_m >= target) xch.found = (uint32_t)(whi - bin) + 1u;
+            cum = b_all;
           }
-          __syncthreads();
-          const double wmass = ctl.z;
-          if (round == 0) target = (double)pp * (wmass + ctl.zb);
-          const int found = window_threshold(win, whi, xmax, target, cum, s);
+          cluster.sync();
+          uint32_t found1 = 0;   // key + 1
+#pragma unroll
+          for (int q = 0; q < kWideCluster; ++q) {
+            const uint32_t f = cluster.map_shared_rank(&xch, q)->found;
+            found1 = f > found1 ? f : found1;
+          }
+          const int found = (int)found1 - 1;
           if (found >= 0) { vstar16 = found; break; }
-          cum += wmass;
           // the next window hangs from the largest key that is present below this one
           const int lo = whi - kWin;
           if (lo < 0) break;
@@ -345,6 +318,17 @@ __global__ void __cluster_dims__(kWideCluster, 1, 1) __launch_bounds__(kThreads,
           }
         }
       };
+      // The noise of the kept vectors is at scattered places of a tensor far larger than the L2: ask
+      // for all of it first, so that the pass below waits for the L2 and not for HBM, vector by vector.
+      if (noise_vec) {
+        for (int i = threadIdx.x; i < myvec; i += blockDim.x) {
+          const uint4 v = vp[i];
+          const __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(bf162_bits(v.x), bf162_bits(v.y)),
+                                               __hmax2_nan(bf162_bits(v.z), bf162_bits(v.w)));
+          if (!__hblt2(m, thr2))
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.noise.dense + nrow * p.noise.stride + ((int64_t)(v0 + i) << 3)));
+        }
+      }
       pass_over(0.f, nullptr);
       // The CTAs agree on the best screened score of the row; what lies within the slack below it
       // are the contenders.  A single contender wins as it stands; otherwise each CTA decides its
