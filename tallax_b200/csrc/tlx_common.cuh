@@ -211,12 +211,14 @@ __device__ __forceinline__ float gumbel_fast(float u) {
   return -logf(-logf(fmaxf(u, kF32Tiny)));
 }
 // Cheapest screening form: hardware log2 for both logs.  -log(u) loses relative accuracy as u -> 1,
-// so the last percent takes the accurate log1p; elsewhere the absolute error stays below 5e-5.
-static __device__ __noinline__ float neg_log_near_one(float u) { return -log1pf(u - 1.0f); }
+// so the last percent takes the series of -log(1 - d), d = 1 - u (exact in f32), to the fourth
+// order (relative error below 1e-8); elsewhere the absolute error of the result stays below 5e-5.
+// Branch-free: a rare slow branch would be paid by the whole warp.
 __device__ __forceinline__ float gumbel_screen(float u) {
   u = fmaxf(u, kF32Tiny);
-  float l = -__logf(u);
-  if (u > 0.99f) l = neg_log_near_one(u);
+  const float d = 1.0f - u;
+  const float series = d * fmaf(d, fmaf(d, fmaf(d, 0.25f, 0.33333334f), 0.5f), 1.0f);
+  const float l = u > 0.99f ? series : -__logf(u);
   return -__logf(l);
 }
 constexpr float kGumbelSlack = 1e-3f;
