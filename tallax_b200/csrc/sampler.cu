@@ -336,6 +336,26 @@ __device__ __forceinline__ int vote_threshold_bin(int my_bin, int want) {
   return lo;
 }
 
+// The same over 16-bit keys (the top halves of the 32-bit keys): 16 votes.
+__device__ __forceinline__ int vote_threshold_key16(int my_key16, int want) {
+  int lo = 0;
+#pragma unroll
+  for (int bit = 15; bit >= 0; --bit) {
+    const int mid = lo | (1 << bit);
+    if (__syncthreads_count(my_key16 >= mid) >= want) lo = mid;
+  }
+  return lo;
+}
+
+// A float that no element with key >= `key` is below (never a NaN pattern): the packed compares
+// screen with it, the exact test is on the keys.
+__device__ __forceinline__ float key_lower_value(uint32_t key) {
+  const uint32_t b = key >> kHistShift;
+  if (b <= 7) return -INFINITY;   // -inf itself lives in bin 7
+  if (b >= 4088) key = 4088u << kHistShift;
+  return key_f32(key);
+}
+
 // Greedy row: this warp's arg-max as key << 32 | (0x7FFFFFFF - local position); positions
 // grow with the column inside a slice, so the lowest position is the lowest column.
 template <int DT>
@@ -674,15 +694,14 @@ __device__ __forceinline__ void scan_tile(const unsigned char* buf, int elems, f
 // indices of those vectors are noted in the warp's list `hits`.  Step 2, once per tile: the
 // listed vectors are looked at densely, one element per lane.
 template <int DT, int WARPS, typename ColOf>
-__device__ __forceinline__ void collect_tile(const unsigned char* buf, int elems, int bin, SelectShared& s,
+__device__ __forceinline__ void collect_tile(const unsigned char* buf, int elems, uint32_t min_key, SelectShared& s,
                                              uint64_t* cand, unsigned short* hits, ColOf col_of) {
   using T = typename Elem<DT>::type;
   constexpr int VEC = 16 / (int)sizeof(T);
   constexpr int kHitCap = kHistBins * 2 / WARPS;    // the idle histogram holds the warps' lists (u16 entries)
   constexpr int kRound = 4;                         // vectors per lane and round
   constexpr int kPerStep = 32 / VEC;                // listed vectors one step of the dense pass covers
-  const float thr = bin_lower_value(bin);
-  const uint32_t min_key = (uint32_t)bin << kHistShift;
+  const float thr = key_lower_value(min_key);
   const int nvec = elems / VEC;
   const uint4* vp = reinterpret_cast<const uint4*>(buf);
   const int lane = lane_id(), w = warp_id();
@@ -1472,6 +1491,7 @@ __global__ void __launch_bounds__(kRowsKThreads, 2) sample_rows_kernel(SamplePar
       // A first threshold that turns out too high (fewer than K candidates at the end of the row)
       // costs one more pass over the row with a lower one, then a second, then the exact select.
       int forced_bin = -1;
+      uint32_t fine_key = 0u;   // first threshold at 16-bit granularity (at or above the lower edge of bin s.bin)
       for (int attempt = 0;; ++attempt) {
       if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
       __syncthreads();
@@ -1494,29 +1514,34 @@ __global__ void __launch_bounds__(kRowsKThreads, 2) sample_rows_kernel(SamplePar
         } else {
           if (t == 0 && forced_bin >= 0) {
             if (threadIdx.x == 0) s.bin = forced_bin;
+            fine_key = 0u;
             __syncthreads();
           } else if (t == 0) {
-            // First threshold, from the maxima of the threads' elements: aim at 1.3 K + 32 elements of
-            // the ROW, i.e. that fraction of this tile.  Too high an estimate is caught at the end
+            // First threshold, from the maxima of the threads' elements: aim at 1.25 K + 48 elements of
+            // the ROW, i.e. that fraction of this tile, at the granularity of 16-bit keys (a whole bin
+            // more than needed can double the candidates).  Too high an estimate is caught at the end
             // (fewer than K candidates), too low a one by the refinement below.
             const int nvec = elems / VEC;
-            const float frac = fminf(1.f, (1.3f * (float)K + 32.f) / (float)n);
+            const float frac = fminf(1.f, (1.25f * (float)K + 48.f) / (float)n);
             const int vec_per_thread = (nvec + (int)blockDim.x - 1) / (int)blockDim.x;
             int vecs = (int)(0.7f / (frac * VEC) + 0.5f);
             vecs = vecs < 1 ? 1 : (vecs > vec_per_thread ? vec_per_thread : vecs);
             const uint32_t tkey = thread_max_key<DT>(buf, nvec, vecs);
-            const int my_bin = ((int)threadIdx.x < nvec) ? (int)(tkey >> kHistShift) : -1;
+            const int my_key16 = ((int)threadIdx.x < nvec) ? (int)(tkey >> 16) : -1;
             const int holders = nvec < (int)blockDim.x ? nvec : (int)blockDim.x;
-            // one standard deviation of the count of holders above the wanted threshold as margin
+            // two and a half standard deviations of the count of holders above the wanted threshold as margin
             float wantf = (float)holders * (1.f - __expf(-(float)(vecs * VEC) * frac));
-            wantf += sqrtf(wantf);
+            wantf += 2.5f * sqrtf(wantf);
             int want = (int)(wantf + 0.999f);
             want = want < 1 ? 1 : (want > holders ? holders : want);
-            const int b0 = (frac >= 0.5f || nvec == 0) ? 0 : vote_threshold_bin(my_bin, want);
-            if (threadIdx.x == 0) s.bin = b0;
+            const int k16 = (frac >= 0.5f || nvec == 0) ? 0 : vote_threshold_key16(my_key16, want);
+            fine_key = (uint32_t)k16 << 16;
+            if (threadIdx.x == 0) s.bin = k16 >> 4;
             __syncthreads();
           }
-          collect_tile<DT, kRowWarps>(buf, elems, s.bin, s, cand, hits, [&](int q) { return g.column(t, q); });
+          const uint32_t bin_key = (uint32_t)s.bin << kHistShift;   // the bin only moves inside the refinement
+          collect_tile<DT, kRowWarps>(buf, elems, bin_key > fine_key ? bin_key : fine_key, s, cand, hits,
+                                      [&](int q) { return g.column(t, q); });
         }
         // The tile is consumed, its buffer is free.  The same barrier carries the decision to raise the
         // threshold, which is due when the candidate list fills up (and once at the end for the sorting
