@@ -26,7 +26,7 @@ if ROOT not in sys.path:
 B, V = 256, 128256          # benchmark configuration: decode batch and vocabulary (Llama-3 sized)
 N_SETS = 4                  # rotating input sets: 4 x 65.7 MB of logits > 126 MB L2, so every step reads HBM
 ALGO_BYTES = B * V * 2 + B * 12 + B * 4   # logits once + three parameter vectors + tokens out
-NCU_TRAFFIC_BYTES = 80805376   # dram__bytes_read.sum + dram__bytes_write.sum over one call's two kernels (profiles/)
+NCU_TRAFFIC_BYTES = 80085760   # dram__bytes_read.sum + dram__bytes_write.sum over one call's two kernels (profiles/)
 METRIC, UNIT = "sampled_tokens_per_s", "tokens/s"
 WORKLOAD = ("fused temperature/top-k/top-p/noise sampling, bf16 logits [256,128256] = N(0,sigma=3) + 10 at 8 "
             "columns per row, T~U[0.5,1.5], top_k~U{1..1024} with 10% disabled, top_p~U[0.6,1), explicit f32 "

@@ -988,16 +988,6 @@ static __device__ __noinline__ int tail_bf16_hist(const SampleParams& p, int64_t
   __syncthreads();
   const int vk_idx = s.tmp_i[0];
   const uint32_t ties_admitted = (uint32_t)s.tmp_i[1], ties_total = (uint32_t)s.tmp_i[2];
-  // The noise of the top-k set is wanted a few thousand cycles from now, at scattered addresses of a
-  // tensor much larger than the L2: ask for it now, so that the mass and threshold steps hide the trip.
-  if (p.noise.dense) {
-    const float* nrow_ptr = p.noise.dense + (row + p.dim0_offset) * p.noise.stride;
-    for (int i = threadIdx.x; i < m; i += blockDim.x) {
-      const uint64_t c = cand[i];
-      if (kmax - (int)(cand_key(c) >> 16) <= vk_idx)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(nrow_ptr + cand_low(c)));
-    }
-  }
   // denominator and top-p threshold over the top-k set
   double mass = 0.0;
   for (int j = 0; j < per; ++j) {
