@@ -53,7 +53,7 @@ constexpr int kChunksPerSlice = kSliceBytes / kChunkBytes;
 constexpr int kRecordCap = 2048;     // candidates (u64) a slice may publish == 16 KB payload
 constexpr int kMergeCap = 4096;      // candidates (u64) held in shared memory
 constexpr int kWin = 2048;           // bf16 histogram window: 16 binades of 16-bit keys below the maximum
-constexpr int kFastK = 1024;         // largest top_k served by the candidate path
+constexpr int kFastK = 2048;         // largest top_k served by the candidate path
 constexpr int kSample = 2048;        // elements of a slice sampled for the first threshold
 constexpr int kMaxSlices = 256;
 constexpr uint32_t kWaitLimit = 1u << 24;  // bounded mbarrier polling
@@ -1540,8 +1540,10 @@ __global__ void __launch_bounds__(kRowsKThreads, 2) sample_rows_kernel(SamplePar
         // a faster warp has already appended from the next tile: so every thread reads it before, and
         // the block takes the OR.
         const int fill_seen = s.fill;
+        // (half the list for the usual top_k; a large top_k fills more than that by itself and waits longer)
+        const int refine_at = 2 * K > kMergeCap / 2 ? (2 * K < kMergeCap - 512 ? 2 * K : kMergeCap - 512) : kMergeCap / 2;
         const int refine_now = __syncthreads_or(
-            cls == kFast && (fill_seen > kMergeCap / 2 || (t == p.S - 1 && DT != TLX_BF16 && fill_seen > 2 * K + 64)));
+            cls == kFast && (fill_seen > refine_at || (t == p.S - 1 && DT != TLX_BF16 && fill_seen > 2 * K + 64)));
         load(t + 2, b);
         if (refine_now) {
           __syncthreads();   // nobody is ahead in the next tile while the fill level is looked at again

@@ -87,7 +87,7 @@ def test_sample_general_path_cases(cuda, dtype):
     exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
     got, status = _run(cuda, x, tk, tp, T, noise=noise)
     _assert_tokens(got, exp, flags, min_checked=0.7)
-    assert (status[[0, 1, 2, 3]] & 1).all()
+    assert (status[[0, 1, 3]] & 1).all()   # no top-k, or one above the candidate path's limit
 
 
 def test_sample_rows_without_top_k_in_a_large_batch(cuda):
