@@ -16,7 +16,9 @@
 //                  the list fills up).  The row finishes inside the CTA: top-k boundary, softmax
 //                  mass and top-p threshold from a histogram over the candidates' keys (bf16;
 //                  sorted candidates for f32), Gumbel arg-max over the kept ones.
-//   cluster kernel (sampler_wide.cuh, bf16 rows whose top-k is disabled) one cluster of eight CTAs
+//                  Rows without any filter (top-k disabled and top_p >= 1) are streamed with their
+//                  noise: Gumbel arg-max over the whole row.
+//   cluster kernel (sampler_wide.cuh, bf16 rows whose top-k is disabled, top_p < 1) one cluster of eight CTAs
 //                  per row keeps the row resident in shared memory; it runs on a side stream
 //                  next to the rows kernel, since the two work on disjoint rows.
 //   When the cluster kernel does not apply (rows not 16-byte aligned, vocabulary too long for the
@@ -1394,6 +1396,72 @@ __global__ void __launch_bounds__(kRowThreads) sample_merge_kernel(SampleParams 
 // histogram shows K collected elements at or above a higher bin.  After the first tile the
 // per-tile work is one packed compare per two elements; everything (candidates, tail, token)
 // stays inside the CTA, so there is no workspace traffic and no second kernel.
+// Rows without any filter: per element the screened score x / T + gumbel(u), the thread's two best.
+struct PlainScore {
+  float a1 = -INFINITY, a2 = -INFINITY, u1 = 0.5f;
+  uint32_t k1 = 0;
+  int c1 = 0x7FFFFFFF;
+  __device__ __forceinline__ void offer(float x, float u, int col, float inv_T) {
+    const float a = x * inv_T + gumbel_screen(u);
+    if (a > a1) { a2 = a1; a1 = a; k1 = f32_key(x); u1 = u; c1 = col; }
+    else if (a > a2) a2 = a;
+  }
+};
+
+// One tile of such a row: the noise of a vector's columns is contiguous (a vector never straddles
+// two chunks), so it comes in with 16-byte loads, two vectors of the thread at a time.
+template <int DT>
+__device__ __forceinline__ void score_tile_plain(const SampleParams& p, const Geometry& g, int t, int64_t nrow,
+                                                 const unsigned char* buf, int elems, float inv_T, PlainScore& sc) {
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  constexpr int kPair = 2;
+  const int nvec = elems / VEC;
+  const uint4* vp = reinterpret_cast<const uint4*>(buf);
+  const bool noise_vec = p.noise.dense && ((reinterpret_cast<uintptr_t>(p.noise.dense) & 15) == 0) &&
+                         ((p.noise.stride & 3) == 0);
+  const float* nbase = p.noise.dense ? p.noise.dense + nrow * p.noise.stride : nullptr;
+  for (int i0 = threadIdx.x; i0 < nvec; i0 += kPair * (int)blockDim.x) {
+    uint4 v[kPair];
+    float4 nz[kPair][VEC / 4];
+    int col0[kPair];
+#pragma unroll
+    for (int u = 0; u < kPair; ++u) {
+      const int i = i0 + u * (int)blockDim.x;
+      col0[u] = -1;
+      if (i < nvec) {
+        v[u] = vp[i];
+        col0[u] = (int)g.column(t, i * VEC);
+        if (noise_vec) {
+#pragma unroll
+          for (int q = 0; q < VEC / 4; ++q) nz[u][q] = __ldg(reinterpret_cast<const float4*>(nbase + col0[u]) + q);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kPair; ++u) {
+      if (col0[u] < 0) continue;
+      T e[VEC];
+      memcpy(e, &v[u], sizeof(uint4));
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        float un;
+        if (noise_vec) {
+          const float4 f = nz[u][j >> 2];
+          un = (j & 3) == 0 ? f.x : (j & 3) == 1 ? f.y : (j & 3) == 2 ? f.z : f.w;
+        } else {
+          un = p.noise.at(nrow, (int64_t)col0[u] + j);
+        }
+        sc.offer(elem_as_float<DT>(e[j]), un, col0[u] + j, inv_T);
+      }
+    }
+  }
+  for (int q = nvec * VEC + threadIdx.x; q < elems; q += blockDim.x) {   // ragged end of the row's last tile
+    const int col = (int)g.column(t, q);
+    sc.offer(elem_as_float<DT>(slice_elem<DT>(buf, q)), p.noise.at(nrow, col), col, inv_T);
+  }
+}
+
 constexpr size_t kRowsSmem = kSharedHeader + kUnionBytes + 2 * (size_t)kSliceBytes + sizeof(Control);
 
 template <int DT>
@@ -1435,14 +1503,42 @@ __global__ void __launch_bounds__(kRowsKThreads, 2) sample_rows_kernel(SamplePar
     const float pp = p.top_p[row], T_ = p.temperature[row];
     int status = 0, tok = 0;
     // rows without top-k only get their threshold here: the final pass is the third kernel's
-    if (DT == TLX_BF16 && p.wide_elsewhere && cls == kGeneral && (int64_t)K >= n) continue;   // the cluster kernel's
+    // No filter at all (top-k disabled, top_p >= 1): a plain Gumbel arg-max over the row, streamed here.
+    const bool plain = cls == kGeneral && (int64_t)K >= n && pp >= 1.0f && !p.have_records;
+    if (DT == TLX_BF16 && p.wide_elsewhere && cls == kGeneral && (int64_t)K >= n && !plain) continue;   // the cluster kernel's
     const bool deferred = DT == TLX_BF16 && cls == kGeneral && (int64_t)K >= n && p.have_records;
     if (!deferred) {
       load(0, 0);
       load(1, 1);
     }
 
-    if (cls == kGeneral) {
+    if (plain) {
+      status = kStatusGeneral;
+      const int64_t nrow = row + p.dim0_offset;
+      PlainScore sc;
+      for (int t = 0; t < p.S; ++t) {
+        const int b = t & 1;
+        if (!mbar_wait(&ctl.mbar[b], (phases >> b) & 1u)) ctl.timeout = 1;
+        phases ^= 1u << b;
+        score_tile_plain<DT>(p, g, t, nrow, slice_base + (size_t)b * kSliceBytes, g.slice_elems(t), 1.0f / T_, sc);
+        __syncthreads();   // the tile is consumed, its buffer is free
+        load(t + 2, b);
+      }
+      // the best screened score and what lies within the slack below it (see tail_bf16_hist)
+      const Best top = block_best(Best{sc.a1, sc.c1}, s);
+      const float cut = top.y - (kGumbelSlack + 1e-5f * fabsf(top.y));
+      const int leaders = __syncthreads_count(sc.a1 >= cut);
+      const int crowded = __syncthreads_or(sc.a2 >= cut);
+      if (crowded || top.tok == 0x7FFFFFFF) {
+        tok = final_argmax<DT>(rowp, n, T_, 0u, false, 0u, 0u, false, p.noise, nrow, s);   // rare: whole-row routine
+      } else if (leaders == 1) {
+        tok = top.tok;
+      } else {
+        Best best{-INFINITY, 0x7FFFFFFF};
+        if (sc.a1 >= cut) best = Best{__fdiv_rn(key_f32(sc.k1), T_) + gumbel_exact(sc.u1), sc.c1};
+        tok = block_best(best, s).tok;
+      }
+    } else if (cls == kGeneral) {
       status = kStatusGeneral;
       bool done = false;
       if constexpr (DT == TLX_BF16) {

@@ -89,7 +89,8 @@ __global__ void __cluster_dims__(kWideCluster, 1, 1) __launch_bounds__(kThreads,
     bool wide = false;
     if (r < p.rows) {
       int K;
-      wide = classify_row(p, r, K) == (int)kGeneral && (int64_t)K >= n;
+      // rows with top_p >= 1 need no histogram: the rows kernel streams them
+      wide = classify_row(p, r, K) == (int)kGeneral && (int64_t)K >= n && p.top_p[r] < 1.0f;
     }
     uint32_t total;
     const uint32_t incl = block_scan_incl<uint32_t>(wide ? 1u : 0u, s.scan_u32, &total, ShflUpU32());
