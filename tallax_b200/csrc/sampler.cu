@@ -2106,7 +2106,10 @@ int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* ca
   const size_t smem = kSharedHeader + (size_t)P * 8;
   int rc;
   if ((rc = ensure_smem((const void*)merge_and_sample_kernel, smem, "merge_and_sample")) != TLX_OK) return rc;
-  merge_and_sample_kernel<<<(unsigned)rows, kMergeThreads, smem, st>>>(
+  // one thread per two (padded) candidates: the sort's stages pair them up, the tail takes two items per thread
+  int threads = P / 2;
+  threads = threads < 64 ? 64 : (threads > kMergeThreads ? kMergeThreads : threads);
+  merge_and_sample_kernel<<<(unsigned)rows, threads, smem, st>>>(
       cand_vals, cand_idx, cand_noise, n_cand, k_per_block, block_stride, row_stride, top_k, top_p, temperature, out_tokens);
   TLX_CHECK_LAUNCH("merge_and_sample");
   return TLX_OK;
