@@ -41,6 +41,7 @@
 // row is streamed again with a lower one; the exact multi-pass select is the last resort.
 // Routines that run once per row or less are kept out of line, which keeps the per-slice loops
 // small in the instruction cache.
+#include <cstdlib>
 #include <mutex>
 
 #include "sampler_general.cuh"
@@ -131,7 +132,24 @@ struct SampleParams {
   // workspace
   int32_t* counters;   // [1] set if a bounded wait gave up
   unsigned char* records;
+  long long* timeline; // timeline builds only: 16 global-timer stamps per CTA (see TLX_STAMP)
 };
+
+// Timeline builds (python -m tallax_b200.build --timeline, a library of its own) record the global timer
+// at marked points of the streaming path's kernels, 16 slots per CTA; other builds compile the marks away.
+#ifdef TLX_TIMELINE
+__device__ __forceinline__ long long global_timer_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define TLX_STAMP(sp, k)                                                                              \
+  do {                                                                                                \
+    if (threadIdx.x == 0 && (sp).timeline) (sp).timeline[(size_t)blockIdx.x * 16 + (k)] = global_timer_ns(); \
+  } while (0)
+#else
+#define TLX_STAMP(sp, k) do {} while (0)
+#endif
 
 struct __align__(16) Control {   // per-CTA bookkeeping in shared memory
   unsigned long long mbar[2];
@@ -964,6 +982,7 @@ static __device__ __noinline__ int tail_bf16_hist(const SampleParams& p, int64_t
   const int kmin = (int)block_min_u32(kmn, s.scan_u32);
   const int W = kmax - kmin + 1;
   if (W > kHistBins) return -1;
+  TLX_STAMP(p, 3);
   uint32_t* win = s.hist;   // win[kmax - key16]
   for (int i = threadIdx.x; i < W; i += blockDim.x) win[i] = 0;
   __syncthreads();
@@ -990,6 +1009,7 @@ static __device__ __noinline__ int tail_bf16_hist(const SampleParams& p, int64_t
   __syncthreads();
   const int vk_idx = s.tmp_i[0];
   const uint32_t ties_admitted = (uint32_t)s.tmp_i[1], ties_total = (uint32_t)s.tmp_i[2];
+  TLX_STAMP(p, 4);
   // denominator and top-p threshold over the top-k set
   double mass = 0.0;
   for (int j = 0; j < per; ++j) {
@@ -1021,6 +1041,7 @@ static __device__ __noinline__ int tail_bf16_hist(const SampleParams& p, int64_t
   const int vstar_idx = s.tmp_i[3];
   const bool cut_ties = vstar_idx == vk_idx && ties_admitted < ties_total;
   __syncthreads();
+  TLX_STAMP(p, 5);
   // the lowest tokens of the boundary group are the admitted ones: list the group's tokens
   uint32_t* tie_tok = s.hist;   // the histogram is no longer needed
   if (cut_ties) {
@@ -1073,10 +1094,12 @@ static __device__ __noinline__ int tail_bf16_hist(const SampleParams& p, int64_t
       }
     }
   }
+  TLX_STAMP(p, 6);
   const Best top = block_best(Best{a1, c1}, s);
   const float cut = top.y - (kGumbelSlack + 1e-5f * fabsf(top.y));
   const int leaders = __syncthreads_count(a1 >= cut);
   const int crowded = __syncthreads_or(a2 >= cut);
+  TLX_STAMP(p, 7);
   // nothing else comes within the slack of the best screened score: it is the winner as it stands
   if (leaders == 1 && !crowded) return top.tok;
   Best best{-INFINITY, 0x7FFFFFFF};
@@ -1199,6 +1222,8 @@ __device__ __forceinline__ int classify_row(const SampleParams& p, int64_t row, 
 
 }  // namespace tlx
 #include "sampler_wide.cuh"
+#include "sampler_stream.cuh"
+#include "sampler_rows.cuh"
 namespace tlx {
 
 // ---- the kernels --------------------------------------------------------------------------
@@ -1913,6 +1938,162 @@ static SliceLayout slice_layout(int64_t vocab, int elem_bytes) {
 // workspace: [flags | one RowState per row | one record per (row, slice)]
 static size_t counters_bytes(int64_t rows) { return 256 + (((size_t)rows * sizeof(RowState) + 255) & ~size_t(255)); }
 
+
+// ---- streaming path (sampler_stream.cuh): workspace layout and launches ---------------------------
+struct StreamLayout {
+  int P, part_chunks, nchunks, nfin;
+  size_t off_desc, off_counts, off_lump, off_flag, off_state, off_records, off_hist, off_cands, off_timeline = 0, bytes;
+};
+static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+static StreamLayout stream_layout(int64_t rows, int64_t vocab) {
+  StreamLayout l;
+  l.nchunks = (int)((vocab * 2 + kStChunk - 1) / kStChunk);
+  l.part_chunks = (l.nchunks + kStMaxParts - 1) / kStMaxParts;
+  if (l.part_chunks < 2) l.part_chunks = 2;
+  l.P = (l.nchunks + l.part_chunks - 1) / l.part_chunks;
+  l.nfin = (int)((vocab * 2 + kFinChunk - 1) / kFinChunk);
+  size_t o = 256;   // [0]: error flag, [1]: item counter
+  l.off_desc = o;    o = align256(o + (size_t)rows * sizeof(StreamDesc));
+  l.off_counts = o;  o = align256(o + (size_t)rows * l.P * kStWarps * sizeof(int));
+  l.off_lump = o;    o = align256(o + (size_t)rows * l.P * sizeof(double));
+  l.off_flag = o;    o = align256(o + (size_t)rows * sizeof(int));
+  l.off_state = o;   o = align256(o + (size_t)rows * sizeof(WideState));
+  l.off_records = o; o = align256(o + (size_t)rows * l.nfin * sizeof(FinRecord));
+  l.off_hist = o;    o = align256(o + (size_t)rows * kStWin * sizeof(uint32_t));
+  l.off_cands = o;   o = align256(o + (size_t)rows * l.P * kStWarps * kStWarpCap * sizeof(uint32_t));
+#ifdef TLX_TIMELINE
+  l.off_timeline = o; o = align256(o + (size_t)4 * 8192 * 16 * sizeof(long long));
+#endif
+  l.bytes = o;
+  return l;
+}
+// bf16 rows that bulk copies can address, long enough for the prologue's sample, few enough for the
+// kernels' per-row tables in shared memory, short enough for 16 parts of at most ten chunks
+static bool stream_path_serves(int dtype, int64_t rows, int64_t vocab, int64_t row_stride, const void* logits) {
+  if (dtype != TLX_BF16 || vocab < kStMinVocab || rows > kStMaxRows) return false;
+  if ((reinterpret_cast<uintptr_t>(logits) & 15) != 0 || ((row_stride * 2) & 15) != 0 || ((vocab * 2) & 15) != 0) return false;
+  return stream_layout(rows, vocab).part_chunks <= kStMaxPartChunks;
+}
+
+// Diagnostic switch for timing the stages of the streaming path one by one (environment variable
+// TLX_SAMPLE_STAGES = 1..3: launch only the first n kernels; +16: the stream kernel only takes the
+// chunks, the streaming floor; +32 / +64: the final pass without its scoring / without its records).
+// Unset in normal use: all three kernels run.
+static int debug_stages() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("TLX_SAMPLE_STAGES");
+    v = e ? atoi(e) : 3;
+    if (v <= 0) v = 3;
+  }
+  return v;
+}
+
+// Launches a kernel that may start while its predecessor on the stream still runs (programmatic dependent
+// launch): the kernel does whatever needs none of the predecessor's results and then executes
+// griddepcontrol.wait, which returns when the predecessor has finished and its writes are visible.  Where
+// the attribute is not accepted the kernel is launched in plain stream order (the wait is then a no-op).
+template <typename... Params, typename... Args>
+static int launch_dependent(void (*kernel)(Params...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                            const char* what, Args... args) {
+  static bool programmatic = getenv("TLX_NO_DEPENDENT_LAUNCH") == nullptr;
+  if (programmatic) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...) == cudaSuccess) {
+      count_launch();
+      return TLX_OK;
+    }
+    cudaGetLastError();
+    programmatic = false;
+  }
+  kernel<<<grid, block, smem, st>>>(static_cast<Params>(args)...);
+  TLX_CHECK_LAUNCH(what);
+  return TLX_OK;
+}
+
+// Row-per-CTA path (sampler_rows.cuh): no workspace; two CTAs per SM, more rows than that are taken in turn.
+static int launch_rows_path(cudaStream_t st, const SampleParams& sp) {
+  const int sms = device_sm_count();
+  RowsParams p{};
+  p.sp = sp;
+  p.nchunks = (int)((sp.vocab * 2 + kRwChunk - 1) / kRwChunk);
+  p.row_bytes = sp.vocab * 2;
+  p.last_nvec = (int)((p.row_bytes - (int64_t)(p.nchunks - 1) * kRwChunk) >> 4);
+  // visiting stride: about half the row (the first two chunks are the sample), coprime to nchunks
+  p.stride = p.nchunks / 2 > 1 ? p.nchunks / 2 : 1;
+  auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
+  while (gcd(p.stride, p.nchunks) != 1) ++p.stride;
+  p.dense_noise = sp.noise.dense && (reinterpret_cast<uintptr_t>(sp.noise.dense) & 15) == 0 && (sp.noise.stride & 3) == 0;
+  p.debug = (debug_stages() >> 4) & 7;
+  int rc;
+  if ((rc = ensure_smem((const void*)sample_rows_stream_kernel, kRwSmemBytes, "sample")) != TLX_OK) return rc;
+  const int64_t cap = 2ll * sms;
+  const int64_t grid = sp.rows < cap ? sp.rows : cap;
+#ifdef TLX_TIMELINE
+  p.sp.timeline = (long long*)sp.counters;   // timeline builds: the caller's workspace receives the stamps
+#endif
+  sample_rows_stream_kernel<<<(unsigned)grid, kRwThreads, kRwSmemBytes, st>>>(p);
+  TLX_CHECK_LAUNCH("sample (rows)");
+  return TLX_OK;
+}
+
+static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* workspace) {
+  const StreamLayout l = stream_layout(sp.rows, sp.vocab);
+  const int stages = debug_stages() & 15;
+  unsigned char* ws = (unsigned char*)workspace;
+  const int sms = device_sm_count();
+  StreamParams p{};
+  p.sp = sp;
+  p.P = l.P; p.part_chunks = l.part_chunks; p.nchunks = l.nchunks; p.nfin = l.nfin; p.row_bytes = sp.vocab * 2;
+  // final-pass CTAs of the finish kernel: what three CTAs per SM leave beside one CTA per row
+  p.fin_ctas = 3 * sms - (int)sp.rows < sms ? sms : 3 * sms - (int)sp.rows;
+  p.error_flag = (int*)ws;
+  p.item_counter = (int*)ws + 1;
+  p.desc = (StreamDesc*)(ws + l.off_desc);
+  p.counts = (int*)(ws + l.off_counts);
+  p.wlump = (double*)(ws + l.off_lump);
+  p.wflag = (int*)(ws + l.off_flag);
+  p.wstate = (WideState*)(ws + l.off_state);
+  p.records = (FinRecord*)(ws + l.off_records);
+  p.whist = (uint32_t*)(ws + l.off_hist);
+  p.cands = (uint32_t*)(ws + l.off_cands);
+  p.debug = (debug_stages() >> 4) & 7;
+  const int64_t items = sp.rows * (int64_t)l.P;
+  const size_t st_smem = kStFixedSmem + (size_t)sp.rows * 6;   // descriptor word and order entry per row
+  const size_t fin_smem = kStFinishFixedSmem + (size_t)sp.rows * sizeof(int);
+  int rc;
+  if ((rc = ensure_smem((const void*)sample_stream_kernel, st_smem, "sample")) != TLX_OK) return rc;
+  if ((rc = ensure_smem((const void*)sample_finish_kernel, fin_smem, "sample")) != TLX_OK) return rc;
+#ifdef TLX_TIMELINE
+  long long* tl = (long long*)(ws + l.off_timeline);
+  p.sp.timeline = tl;
+#define TLX_TIMELINE_KERNEL(k) p.sp.timeline = tl + (size_t)(k) * 8192 * 16
+#else
+#define TLX_TIMELINE_KERNEL(k) do {} while (0)
+#endif
+  sample_prologue_kernel<<<(unsigned)sp.rows, kStProThreads, 0, st>>>(p);
+  TLX_CHECK_LAUNCH("sample (prologue)");
+  if (stages < 2) return TLX_OK;
+  const int64_t sgrid = items < 4ll * sms ? items : 4ll * sms;
+  TLX_TIMELINE_KERNEL(1);
+  if ((rc = launch_dependent(sample_stream_kernel, (unsigned)sgrid, kStThreads, st_smem, st, "sample (stream)", p)) != TLX_OK) return rc;
+  if (stages < 3) return TLX_OK;
+  // the noise tensor can be streamed next to the logits if its rows start on 16-byte boundaries
+  const int dense = sp.noise.dense && (reinterpret_cast<uintptr_t>(sp.noise.dense) & 15) == 0 && (sp.noise.stride & 3) == 0;
+  TLX_TIMELINE_KERNEL(2);
+  return launch_dependent(sample_finish_kernel, (unsigned)(p.fin_ctas + sp.rows), kStThreads, fin_smem, st,
+                          "sample (finish)", p, dense);
+}
+
 }  // namespace tlx
 
 using namespace tlx;
@@ -1922,7 +2103,9 @@ extern "C" {
 size_t tlx_sample_workspace_bytes(int64_t rows, int64_t vocab) {
   if (rows <= 0 || vocab <= 0) return 0;
   const SliceLayout l = slice_layout(vocab, 4);  // the widest supported element
-  return counters_bytes(rows) + (size_t)rows * l.S * kRecordBytes;
+  const size_t sliced = counters_bytes(rows) + (size_t)rows * l.S * kRecordBytes;
+  const size_t streamed = stream_layout(rows, vocab).bytes;
+  return sliced > streamed ? sliced : streamed;
 }
 
 int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab, int64_t row_stride,
@@ -1961,6 +2144,14 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
   p.counters = (int32_t*)workspace;
   p.rowstate = reinterpret_cast<RowState*>((unsigned char*)workspace + 256);
   p.records = (unsigned char*)workspace + counters_bytes(rows);
+
+  if (stream_path_serves(dtype, rows, vocab, row_stride, logits)) {
+    // at least about one row per SM: a CTA per row; fewer: the rows are split over the CTAs
+    const char* force = getenv("TLX_SAMPLE_PATH");   // diagnostic: "rows" or "split"
+    const bool by_rows = force ? force[0] == 'r' : 2 * rows >= device_sm_count();
+    if (by_rows) return launch_rows_path(st, p);
+    if (workspace_bytes >= stream_layout(rows, vocab).bytes) return launch_stream_path(st, p, workspace);
+  }
 
   const int64_t items = rows * l.S;
   const int64_t slots = 2ll * device_sm_count();
