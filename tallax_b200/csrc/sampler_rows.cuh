@@ -33,16 +33,17 @@
 
 namespace tlx {
 
-constexpr int kRwThreads = 512;
+constexpr int kRwThreads = 256;
 constexpr int kRwWarps = kRwThreads / 32;
 constexpr int kRwChunk = 16384;                       // bytes per bulk copy and ring slot
 constexpr int kRwChunkElems = kRwChunk / 2;
 constexpr int kRwChunkVecs = kRwChunk / 16;
 constexpr int kRwVecPerThread = kRwChunkVecs / kRwThreads;   // 2
 constexpr int kRwSlots = 4;
-constexpr int kRwWarpCap = 256;                       // candidates per warp and row
+constexpr int kRwWarpCap = 512;                       // candidates per warp and row
 constexpr int kRwCap = kRwWarpCap * kRwWarps;         // 4096
 constexpr int kRwBins = kStWin;                       // histogram bins: a wide row's window, or keys above a normal row's threshold
+constexpr int kRwKeys = kStSample / kRwThreads;          // sample keys per thread
 constexpr int kRwSelBins = 2048;                      // threshold selection: keys below the sample's maximum that are told apart
 constexpr int kRwDenseElems = 4096;                   // dense pass: elements per group (8 KB of logits + 16 KB of noise)
 constexpr int kRwDenseGroups = 2;
@@ -143,16 +144,16 @@ __device__ __forceinline__ bool rw_pass(const RowsParams& p, const unsigned char
   return true;
 }
 
-// The r-th largest of the 8 keys each thread holds (4096 in all): a histogram of the keys in the
+// The r-th largest of the kRwKeys keys each thread holds (4096 in all): a histogram of the keys in the
 // kRwSelBins-key window below the sample's maximum (`bins`: that many words of shared memory, any
 // contents), scanned from the top.  If fewer than r keys lie in the window, its lowest key is returned
 // (a threshold that is lower than asked for).  r in [1, 4096].  All threads call.
-static __device__ __noinline__ int rw_select_key(const uint32_t (&key)[8], int r, uint32_t* bins, RwControl& ctl) {
+__device__ __forceinline__ int rw_select_key(const uint32_t (&key)[kRwKeys], int r, uint32_t* bins, RwControl& ctl) {
   constexpr int kPer = kRwSelBins / kRwThreads;   // 4
   const int lane = lane_id(), warp = warp_id();
   uint32_t m = key[0];
 #pragma unroll
-  for (int i = 1; i < 8; ++i) m = max(m, key[i]);
+  for (int i = 1; i < kRwKeys; ++i) m = max(m, key[i]);
   m = __reduce_max_sync(0xFFFFFFFFu, m);
   if (lane == 0) ctl.red[warp] = (int)m;
 #pragma unroll
@@ -162,7 +163,7 @@ static __device__ __noinline__ int rw_select_key(const uint32_t (&key)[8], int r
 #pragma unroll
   for (int w = 1; w < kRwWarps; ++w) top = max(top, ctl.red[w]);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < kRwKeys; ++i) {
     const int d = top - (int)key[i];
     if (d < kRwSelBins) atomicAdd(&bins[d], 1u);
   }
@@ -276,7 +277,7 @@ struct RwKeep {
 
 // Gumbel arg-max over the kept candidates of the warps' lists (wc: this warp's count): screened in f32,
 // decided on the f64-evaluated Gumbel term when several candidates come within the slack.  All threads call.
-static __device__ __noinline__ int rw_score_lists(const SampleParams& sp, int64_t nrow, float T_, RwKeep keep,
+__device__ __forceinline__ int rw_score_lists(const SampleParams& sp, int64_t nrow, float T_, RwKeep keep,
                                                   RwSmem& sm, int wc) {
   const int lane = lane_id(), warp = warp_id();
   const uint32_t* wtok = sm.tok + warp * kRwWarpCap;
@@ -286,19 +287,20 @@ static __device__ __noinline__ int rw_score_lists(const SampleParams& sp, int64_
   uint32_t b1 = 0;
   int t1 = 0x7FFFFFFF;
 #pragma unroll 1
-  for (int i0 = lane; i0 < wc; i0 += 4 * 32) {
-    float uu[4];
-    bool kk[4];
+  for (int i0 = lane; i0 < wc; i0 += 8 * 32) {
+    float uu[8];
+    uint32_t kk = 0;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int i = i0 + u * 32;
-      kk[u] = i < wc && keep(wtok[i], wbits[i]);
-      uu[u] = kk[u] ? sp.noise.at(nrow, (int64_t)wtok[i]) : 0.5f;
+      const bool k = i < wc && keep(wtok[i], wbits[i]);
+      kk |= (k ? 1u : 0u) << u;
+      uu[u] = k ? sp.noise.at(nrow, (int64_t)wtok[i]) : 0.5f;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int i = i0 + u * 32;
-      if (kk[u]) {
+      if (kk & (1u << u)) {
         const uint32_t b = wbits[i];
         const float a = fmaf(__uint_as_float(b << 16), inv_T, gumbel_screen(uu[u]));
         const int tk = (int)wtok[i];
@@ -340,7 +342,7 @@ static __device__ __noinline__ int rw_score_lists(const SampleParams& sp, int64_
 // Tail of a normal row over the warps' candidate lists (all taken at or above the key thr16).  Returns
 // the token, or -1 if the lists cannot be trusted to hold the row's top-K or the candidates' keys spread
 // over more than kRwBins values.  hist[] must be zero.  All threads call.
-static __device__ __noinline__ int rw_tail_normal(const SampleParams& sp, int64_t nrow, int K, int thr16, float pp, float T_,
+__device__ __forceinline__ int rw_tail_normal(const SampleParams& sp, int64_t nrow, int K, int thr16, float pp, float T_,
                                                   RwSmem& sm, int wc) {
   RwControl& ctl = *sm.ctl;
   const int lane = lane_id(), warp = warp_id();
@@ -480,7 +482,7 @@ static __device__ __noinline__ int rw_tail_normal(const SampleParams& sp, int64_
 // followed by their 16 KB of noise): arg-max of x / T + gumbel(u) over the elements that are not below tvf
 // (all of them if tvf is a NaN).  Needs p.dense_noise; the ring must be idle.  Returns the token; all
 // threads call.
-static __device__ __noinline__ int rw_dense_pass(const RowsParams& p, int64_t row, float T_, float tvf, __nv_bfloat162 tv2,
+__device__ __forceinline__ int rw_dense_pass(const RowsParams& p, int64_t row, float T_, float tvf, __nv_bfloat162 tv2,
                                                  RwSmem& sm, uint32_t& phases, bool& ok) {
   constexpr int kGroupBytes = kRwDenseElems * 6;
   const SampleParams& sp = p.sp;
@@ -514,8 +516,8 @@ static __device__ __noinline__ int rw_dense_pass(const RowsParams& p, int64_t ro
     const float* nbuf = reinterpret_cast<const float*>(buf + kRwDenseElems * 2);
     const int64_t rest = sp.vocab - (int64_t)c * kRwDenseElems;
     const int nvec = (int)((rest < kRwDenseElems ? rest : kRwDenseElems) >> 3);
-    const int v = threadIdx.x;   // one vector per thread and group
-    if (v < nvec) {
+#pragma unroll 1
+    for (int v = threadIdx.x; v < nvec; v += kRwThreads) {
       const uint4 x = *reinterpret_cast<const uint4*>(buf + (size_t)v * 16);
       const __nv_bfloat162 m =
           __hmax2_nan(__hmax2_nan(bf162_bits(x.x), bf162_bits(x.y)), __hmax2_nan(bf162_bits(x.z), bf162_bits(x.w)));
@@ -634,16 +636,20 @@ __global__ void __launch_bounds__(kRwThreads, 2) sample_rows_stream_kernel(RowsP
       // the sample: 4096 elements out of the first two chunks requested (the visiting order spreads them
       // over the row); the later copies keep arriving while the threshold is worked out
       const int primed_chunks = p.nchunks < 2 ? p.nchunks : 2;
-      const int sl = (int)threadIdx.x % primed_chunks;
-      mbar_wait_suspended(&ctl.mbar[sl], (phases >> sl) & 1u);   // the pass waits for it again (and checks)
-      const int nvec = rw_chunk_of(p, sl) == p.nchunks - 1 ? p.last_nvec : kRwChunkVecs;
-      int v = ((int)threadIdx.x / primed_chunks) * (kRwChunkVecs * primed_chunks / kRwThreads);
-      v = v < nvec ? v : v % nvec;
-      const uint4 x = *reinterpret_cast<const uint4*>(sm.ring + (size_t)sl * kRwChunk + (size_t)v * 16);
-      const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
-      uint32_t key[8];
+      uint32_t key[kRwKeys];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) key[e] = bf16_key16((e & 1) ? (w4[e >> 1] >> 16) : (w4[e >> 1] & 0xFFFFu));
+      for (int j = 0; j < kRwKeys / 8; ++j) {
+        const int idx = (int)threadIdx.x + j * kRwThreads;   // 512 sample vectors
+        const int sl = idx % primed_chunks;
+        mbar_wait_suspended(&ctl.mbar[sl], (phases >> sl) & 1u);   // the pass waits for it again (and checks)
+        const int nvec = rw_chunk_of(p, sl) == p.nchunks - 1 ? p.last_nvec : kRwChunkVecs;
+        int v = (idx / primed_chunks) * (kRwChunkVecs * primed_chunks / 512);
+        v = v < nvec ? v : v % nvec;
+        const uint4 x = *reinterpret_cast<const uint4*>(sm.ring + (size_t)sl * kRwChunk + (size_t)v * 16);
+        const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) key[j * 8 + e] = bf16_key16((e & 1) ? (w4[e >> 1] >> 16) : (w4[e >> 1] & 0xFFFFu));
+      }
       int r = 1;   // wide rows: the sample's maximum
       if (cls == kRwNormal) {
         // rank in the sample that leaves, with four standard deviations of margin, at least K elements of
@@ -676,6 +682,12 @@ __global__ void __launch_bounds__(kRwThreads, 2) sample_rows_stream_kernel(RowsP
       });
       primed = false;
       TLX_STAMP(sp, 2);
+      if (ok && sp.noise.dense && T_ >= kSamplingEps) {
+        // most of the candidates' noise is wanted two microseconds from now: start it on its way to L2
+        const float* nr = sp.noise.dense + nrow * sp.noise.stride;
+        const int n = wc < kRwWarpCap ? wc : kRwWarpCap;
+        for (int i = lane; i < n; i += 32) prefetch_l2(nr + wtok[i]);
+      }
       if (ok) tok = rw_tail_normal(sp, nrow, K, key16, pp, T_, sm, wc);
       TLX_STAMP(sp, 3);
 #ifdef TLX_TIMELINE_TWICE

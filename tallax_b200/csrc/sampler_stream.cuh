@@ -175,7 +175,7 @@ constexpr size_t kStFixedSmem = kStRingBytes + kStAreaBytes + kStListBytes + siz
 // element above the window or a NaN; a maximum too far below the window top; a threshold below the
 // window).  All NT threads call; thread t owns the bins [t * kStWin / NT, (t + 1) * kStWin / NT).
 template <int NT>
-static __device__ __noinline__ int wide_threshold_core(int wtop, float pp, const uint32_t* hist, double lump_thread,
+__device__ __forceinline__ int wide_threshold_core(int wtop, float pp, const uint32_t* hist, double lump_thread,
                                                        int bad_thread, WideScratch& ws) {
   constexpr int kPer = kStWin / NT;   // ascending i = descending key
   constexpr int kNW = NT / 32;

@@ -312,19 +312,24 @@ int tlx_sort_static(void* stream, const void* keys, int dtype, int64_t rows, int
   // In host code the array's name is only a handle: the device address is looked up once per
   // device (with that device current) and remembered.
   static void* device_address[64] = {};
+  static std::mutex address_mutex;   // host threads may make their first calls at the same time
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "sort_static: cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= 64) return set_error(TLX_ERR_UNSUPPORTED, "sort_static: device ordinal %d not supported", dev);
-  if (!device_address[dev]) {
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_static_sort_scratch);
-    if (e != cudaSuccess || !ptr)
-      return set_error(TLX_ERR_CUDA, "sort_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    device_address[dev] = ptr;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(address_mutex);
+    if (!device_address[dev]) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_static_sort_scratch);
+      if (e != cudaSuccess || !ptr)
+        return set_error(TLX_ERR_CUDA, "sort_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      device_address[dev] = ptr;
+    }
+    scratch = device_address[dev];
   }
-  return tlx_sort(stream, keys, dtype, rows, n, descending, in_perm, out_keys, out_perm, device_address[dev],
-                  kStaticSortBytes);
+  return tlx_sort(stream, keys, dtype, rows, n, descending, in_perm, out_keys, out_perm, scratch, kStaticSortBytes);
 }
 
 }  // extern "C"
