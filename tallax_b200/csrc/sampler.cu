@@ -2066,13 +2066,28 @@ static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* wor
   p.records = (FinRecord*)(ws + l.off_records);
   p.whist = (uint32_t*)(ws + l.off_hist);
   p.cands = (uint32_t*)(ws + l.off_cands);
-  p.debug = (debug_stages() >> 4) & 7;
+  p.debug = (debug_stages() >> 4) & 31;
   const int64_t items = sp.rows * (int64_t)l.P;
   const size_t st_smem = kStFixedSmem + (size_t)sp.rows * 6;   // descriptor word and order entry per row
   const size_t fin_smem = kStFinishFixedSmem + (size_t)sp.rows * sizeof(int);
   int rc;
   if ((rc = ensure_smem((const void*)sample_stream_kernel, st_smem, "sample")) != TLX_OK) return rc;
   if ((rc = ensure_smem((const void*)sample_finish_kernel, fin_smem, "sample")) != TLX_OK) return rc;
+  // An SM changes its split between L1 and shared memory only while idle: the three kernels ask for the same
+  // split, so that each one's CTAs can move in beside those of the one before.
+  {
+    static std::mutex mu;
+    static bool done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+      cudaFuncSetAttribute((const void*)sample_prologue_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      cudaFuncSetAttribute((const void*)sample_stream_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      cudaFuncSetAttribute((const void*)sample_finish_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      done[dev] = true;
+    }
+  }
 #ifdef TLX_TIMELINE
   long long* tl = (long long*)(ws + l.off_timeline);
   p.sp.timeline = tl;
@@ -2083,7 +2098,8 @@ static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* wor
   sample_prologue_kernel<<<(unsigned)sp.rows, kStProThreads, 0, st>>>(p);
   TLX_CHECK_LAUNCH("sample (prologue)");
   if (stages < 2) return TLX_OK;
-  const int64_t sgrid = items < 4ll * sms ? items : 4ll * sms;
+  int64_t sgrid = items < 4ll * sms ? items : 4ll * sms;
+  sgrid -= sgrid % l.P;   // whole rows in the first wave (see sample_stream_kernel)
   TLX_TIMELINE_KERNEL(1);
   if ((rc = launch_dependent(sample_stream_kernel, (unsigned)sgrid, kStThreads, st_smem, st, "sample (stream)", p)) != TLX_OK) return rc;
   if (stages < 3) return TLX_OK;
@@ -2146,9 +2162,10 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
   p.records = (unsigned char*)workspace + counters_bytes(rows);
 
   if (stream_path_serves(dtype, rows, vocab, row_stride, logits)) {
-    // at least about one row per SM: a CTA per row; fewer: the rows are split over the CTAs
-    const char* force = getenv("TLX_SAMPLE_PATH");   // diagnostic: "rows" or "split"
-    const bool by_rows = force ? force[0] == 'r' : 2 * rows >= device_sm_count();
+    // the rows are split over the CTAs; the row-per-CTA kernel is kept for comparison (diagnostic switch
+    // TLX_SAMPLE_PATH=rows): it is faster on batches without wide rows and much slower with them
+    const char* force = getenv("TLX_SAMPLE_PATH");
+    const bool by_rows = force && force[0] == 'r';
     if (by_rows) return launch_rows_path(st, p);
     if (workspace_bytes >= stream_layout(rows, vocab).bytes) return launch_stream_path(st, p, workspace);
   }

@@ -47,7 +47,7 @@ constexpr int kStVecPerThread = kStChunkVecs / kStThreads;    // 3
 constexpr int kStMaxParts = 16;                      // parts per row
 constexpr int kStMaxPartChunks = 10;                 // 61440 elements: a position inside a part fits 16 bits
 constexpr int kStWarpCap = 128;                      // candidates one warp may publish per item
-constexpr int kStSpec = 64;                          // entries of a segment the finish kernel fetches before it knows the count
+constexpr int kStSpec = 32;                          // entries of a segment the finish kernel fetches before it knows the count
 constexpr int kStMaxK = 1024;                        // largest top_k served by the candidate lists
 constexpr int kStWinExtra = 512;                     // window top = sample maximum + this many keys
 constexpr int kStWin = kWin + kStWinExtra;           // bins per wide row in the workspace
@@ -63,7 +63,7 @@ constexpr int kFinSlots = 2;
 constexpr int kFinVecPerThread = kFinChunk / 16 / kStThreads;   // 2
 static_assert(kStMaxPartChunks * kStChunkElems <= 65536, "candidate positions are 16 bits");
 static_assert(kStChunkVecs % kStThreads == 0 && kFinChunk / 16 % kStThreads == 0, "whole vectors per thread");
-static_assert(kStMaxParts * kStWarps * (kStSpec / 16) <= 2 * kStThreads, "two rounds of speculative fetches per thread");
+static_assert(kStMaxParts * kStWarps * (kStSpec / 16) <= kStThreads, "one round of speculative fetches per thread");
 
 enum StClass : int { kStNormal = 0, kStWide = 1, kStOther = 2 };
 
@@ -78,7 +78,7 @@ struct __align__(16) WideState {
   int vstar16;               // kept: value >= the value of this key; -1: the window did not settle the threshold
   int parts_done;            // stream kernel: parts of the row whose totals are in
   int done;                  // final pass: ranges that have delivered their record
-  int pad;
+  int kmax16;                // key of the row's greatest element (valid with vstar16 >= 0)
 };
 static_assert(sizeof(WideState) == 16, "WideState layout");
 
@@ -144,7 +144,8 @@ struct __align__(16) WideScratch {
   double dlump[16];
   int first[16];
   int vstar;
-  int pad[3];
+  int kmax16;   // out: key of the greatest element
+  int pad[2];
 };
 
 // Small per-CTA scratch shared by the kernels' block-wide steps.
@@ -154,7 +155,7 @@ struct __align__(16) StControl {
   int cnt;
   int flag;
   int vstar;
-  int pad;
+  uint32_t best_key;      // final pass: the CTA's best screened score so far, as an ordered key
   double dsum[kStWarps];
   double dlump[kStWarps];
   uint32_t wkey[kStWarps];
@@ -210,7 +211,7 @@ __device__ __forceinline__ int wide_threshold_core(int wtop, float pp, const uin
     il += shfl_xor_f64(il, o);
   }
   if (lane == 31) { ws.dsum[warp] = im; ws.dlump[warp] = il; }
-  if (threadIdx.x == 0) ws.vstar = -1;
+  if (threadIdx.x == 0) { ws.vstar = -1; ws.kmax16 = kmax16; }
   __syncthreads();
   double total = 0.0, below = 0.0;
   for (int w = 0; w < kNW; ++w) {
@@ -299,9 +300,10 @@ __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamPa
     for (int round = 0; round < 16 && hi - lo > 1; ++round) {
       const int mid = (lo + hi) >> 1;
       const __nv_bfloat162 t2 = bf162_splat_bits(key16_bf16_bits((uint32_t)mid));
-      __nv_bfloat162 acc = bf162_bits(0u);
+      __nv_bfloat162 acc4[4] = {bf162_bits(0u), bf162_bits(0u), bf162_bits(0u), bf162_bits(0u)};
 #pragma unroll
-      for (int i = 0; i < kStSampleVecs * 4; ++i) acc = __hadd2(acc, __hgeu2(h[i], t2));
+      for (int i = 0; i < kStSampleVecs * 4; ++i) acc4[i & 3] = __hadd2(acc4[i & 3], __hgeu2(h[i], t2));
+      const __nv_bfloat162 acc = __hadd2(__hadd2(acc4[0], acc4[1]), __hadd2(acc4[2], acc4[3]));
       int c = (int)(__low2float(acc) + __high2float(acc) + 0.5f);
       c = __reduce_add_sync(0xFFFFFFFFu, c);
       if (lane == 0) red[round & 1][warp] = c;
@@ -402,7 +404,7 @@ __device__ __forceinline__ void st_filter_chunk(const unsigned char* buf, int nv
 template <bool kFull, int NT = kStThreads, int VPT = kStVecPerThread>
 __device__ __forceinline__ void st_hist_chunk(const unsigned char* buf, int nvec, int wtop, float nxl, uint32_t* win,
                                               float& lump, int& above) {
-#pragma unroll
+#pragma unroll 1
   for (int j = 0; j < VPT; ++j) {
     const int v = (int)threadIdx.x + j * NT;
     if (kFull || v < nvec) {
@@ -430,14 +432,34 @@ __device__ __forceinline__ void st_hist_chunk(const unsigned char* buf, int nvec
 
 // The producer's state (thread 0): the item whose chunks are being requested, and the one claimed for
 // afterwards (its value is first used an item later, so the counter's round trip stays off the path).
-// Item i is part (i % P) of the row order[i / P]: the wide rows come first (their items take longest),
-// then the normal rows; rows of class "other" are not streamed.  A CTA starts on the item of its own
-// index and claims further ones from the counter.
+// Items: the first gridDim.x of them (one per CTA, no claim needed) are the parts of the first
+// gridDim.x / P rows in their natural order, so that their copies can be requested before anything about
+// the rows is known.  The items claimed from the counter are the parts of the remaining rows: those of the
+// wide rows (they take longest) early, but only every third item, so that an SM rarely works on several
+// of them at a time; rows of class "other" are not streamed.
 struct StProducer {
-  int item;    // >= 0: item index; -1: no more
+  int item;    // >= 0: there is an item; -1: no more
   int row, part, chunk;
-  int next;
+  int next;    // claimed index (0, 1, ... among the claimed items)
   int pushed;
+};
+
+struct StOrder {
+  const unsigned short* rows;   // the wide rows behind the first wave, then the normal ones
+  int nwide_items, nnormal_items;
+  // claimed index -> row << 8 | part, or -1 past the end
+  __device__ __forceinline__ int item(int j, int P) const {
+    if (j >= nwide_items + nnormal_items) return -1;
+    int idx;   // index into the wide items (< nwide_items) or nwide_items + index into the normal items
+    if (nnormal_items >= 2 * nwide_items) {
+      if (j < 3 * nwide_items) idx = j % 3 == 0 ? j / 3 : nwide_items + (j - j / 3 - 1);
+      else idx = j;
+    } else {
+      idx = j;   // too few normal items to spread the wide ones: wide first
+    }
+    const int r = idx / P;   // both lists hold whole rows, the wide rows' entries come first
+    return ((int)rows[r] << 8) | (idx - r * P);
+  }
 };
 
 __device__ __forceinline__ int st_part_chunks(const StreamParams& p, int part) {
@@ -445,24 +467,8 @@ __device__ __forceinline__ int st_part_chunks(const StreamParams& p, int part) {
   return rest < p.part_chunks ? rest : p.part_chunks;
 }
 
-// Requests the next chunk into `slot` (thread 0 only).
-__device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, int items, const unsigned short* order,
-                                         unsigned char* ring, StControl& ctl, int slot) {
-  for (;;) {
-    if (ps.item < 0) return;
-    if (ps.chunk < st_part_chunks(p, ps.part)) break;
-    const int nxt = ps.next;
-    ps.item = nxt < items ? nxt : -1;
-    if (ps.item >= 0) {
-      const int r = nxt / p.P;
-      ps.part = nxt - r * p.P;
-      ps.row = order[r];
-      ps.chunk = 0;
-      ps.next = (int)gridDim.x + atomicAdd(p.item_counter, 1);
-    }
-    ctl.fifo[ps.pushed & 7] = ps.item < 0 ? -1 : (ps.row << 8) | ps.part;
-    ps.pushed++;
-  }
+__device__ __forceinline__ void st_issue_chunk(const StreamParams& p, StProducer& ps, unsigned char* ring, StControl& ctl,
+                                               int slot) {
   const int c = ps.part * p.part_chunks + ps.chunk;
   const int64_t off = (int64_t)c * kStChunk;
   const int64_t rest = p.row_bytes - off;
@@ -474,7 +480,28 @@ __device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, 
   ps.chunk++;
 }
 
+// Requests the next chunk into `slot` (thread 0 only).
+__device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, const StOrder& order, unsigned char* ring,
+                                         StControl& ctl, int slot) {
+  for (;;) {
+    if (ps.item < 0) return;
+    if (ps.chunk < st_part_chunks(p, ps.part)) break;
+    const int code = order.item(ps.next, p.P);
+    ps.item = code;
+    if (code >= 0) {
+      ps.row = code >> 8;
+      ps.part = code & 0xFF;
+      ps.chunk = 0;
+      ps.next = atomicAdd(p.item_counter, 1);
+    }
+    ctl.fifo[ps.pushed & 7] = code;
+    ps.pushed++;
+  }
+  st_issue_chunk(p, ps, ring, ctl, slot);
+}
+
 // Shared memory beyond the fixed part: per row 4 bytes of descriptor (class << 16 | key) and 2 bytes of order.
+// The grid is a multiple of P (whole rows in the first wave) and at most rows * P.
 __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamParams p) {
   extern __shared__ __align__(128) unsigned char st_smem[];
   unsigned char* ring = st_smem;
@@ -483,56 +510,66 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
       reinterpret_cast<unsigned short*>(st_smem + kStRingBytes + kStAreaBytes) + warp_id() * (32 * kStVecPerThread);
   StControl& ctl = *reinterpret_cast<StControl*>(st_smem + kStRingBytes + kStAreaBytes + kStListBytes);
   uint32_t* dtab = reinterpret_cast<uint32_t*>(st_smem + kStFixedSmem);
-  unsigned short* order = reinterpret_cast<unsigned short*>(dtab + p.sp.rows);
+  unsigned short* order_rows = reinterpret_cast<unsigned short*>(dtab + p.sp.rows);
   const int rows = (int)p.sp.rows;
   const int lane = lane_id(), warp = warp_id();
+  const int first_rows = (int)(gridDim.x / (unsigned)p.P);
   TLX_STAMP(p.sp, 0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the finish kernel's CTAs move in as these leave
+  // the first item's copies need nothing but the CTA's index
+  StProducer ps;
+  ps.item = 0;
+  ps.row = (int)(blockIdx.x / (unsigned)p.P);
+  ps.part = (int)(blockIdx.x % (unsigned)p.P);
+  ps.chunk = 0;
+  ps.next = 0;
+  ps.pushed = 1;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStSlots; ++s) mbar_init(&ctl.mbar[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    ctl.fifo[0] = (ps.row << 8) | ps.part;
+    const int nc0 = st_part_chunks(p, ps.part);
+    for (int s = 0; s < kStSlots && s < nc0; ++s) st_issue_chunk(p, ps, ring, ctl, s);
   }
   // everything below reads what the prologue kernel wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  // descriptor table; the wide rows' indices go to the front of `order`, the normal rows' behind them
+  TLX_STAMP(p.sp, 6);
+  if (threadIdx.x == 0) ps.next = atomicAdd(p.item_counter, 1);   // used after the lists below are built
   for (int r = threadIdx.x; r < rows; r += kStThreads) {
     const StreamDesc d = p.desc[r];
     dtab[r] = ((uint32_t)d.cls << 16) | (uint32_t)d.key16;
   }
   __syncthreads();
-  int nstream = 0;   // rows placed so far
+  TLX_STAMP(p.sp, 7);
+  // the rows behind the first wave: the wide ones to the front of the list, the normal ones behind them
+  int nlisted = 0, nwide = 0;
   for (int pass = 0; pass < 2; ++pass) {
     const uint32_t want = pass == 0 ? (uint32_t)kStWide : (uint32_t)kStNormal;
-    for (int base = 0; base < rows; base += kStThreads) {
+    for (int base = first_rows; base < rows; base += kStThreads) {
       const int r = base + (int)threadIdx.x;
       const bool take = r < rows && (dtab[r] >> 16) == want;
       const uint32_t mask = __ballot_sync(0xFFFFFFFFu, take);
       if (lane == 0) ctl.ibest[warp] = __popc(mask);
       __syncthreads();
-      int off = nstream, total = 0;
+      int off = nlisted, total = 0;
 #pragma unroll
       for (int w = 0; w < kStWarps; ++w) {
         if (w < warp) off += ctl.ibest[w];
         total += ctl.ibest[w];
       }
-      if (take) order[off + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)r;
-      nstream += total;
+      if (take) order_rows[off + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)r;
+      nlisted += total;
       __syncthreads();
     }
+    if (pass == 0) nwide = nlisted;
   }
-  const int items = nstream * p.P;
-  if ((int)blockIdx.x >= items) return;
-  StProducer ps;
-  ps.item = blockIdx.x;
-  ps.part = (int)(blockIdx.x % (unsigned)p.P);
-  ps.row = order[blockIdx.x / (unsigned)p.P];
-  ps.chunk = 0;
-  ps.next = 0;
-  ps.pushed = 1;
+  StOrder order;
+  order.rows = order_rows;
+  order.nwide_items = nwide * p.P;
+  order.nnormal_items = (nlisted - nwide) * p.P;
   if (threadIdx.x == 0) {
-    ctl.fifo[0] = (ps.row << 8) | ps.part;
-    ps.next = (int)gridDim.x + atomicAdd(p.item_counter, 1);
-    for (int s = 0; s < kStSlots; ++s) st_issue(p, ps, items, order, ring, ctl, s);
+    // a first item shorter than the ring: go on into the claimed items
+    for (int s = ps.chunk; s < kStSlots; ++s) st_issue(p, ps, order, ring, ctl, s);
   }
   __syncthreads();
 
@@ -579,9 +616,12 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         return;
       }
       // the chunk is consumed, its slot is free
-      if (threadIdx.x == 0) st_issue(p, ps, items, order, ring, ctl, slot);
+      if (threadIdx.x == 0) st_issue(p, ps, order, ring, ctl, slot);
       if (++slot == kStSlots) { slot = 0; phase ^= 1u; }
     }
+#ifdef TLX_TIMELINE
+    long long tl_t = global_timer_ns();
+#endif
     if (cls == kStNormal) {
       if (lane == 0) p.counts[seg] = wc;
     } else if (cls == kStWide) {
@@ -596,8 +636,7 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
       for (int o = 16; o > 0; o >>= 1) l += shfl_xor_f64(l, o);
       if (lane == 0) ctl.dsum[warp] = l;
       if (above < 0) p.wflag[row] = 1;
-      __threadfence();
-      __syncthreads();
+      __syncthreads();   // with thread 0's fence below: every thread's additions come before the count
       if (threadIdx.x == 0) {
         double t = 0.0;
         for (int w = 0; w < kStWarps; ++w) t += ctl.dsum[w];
@@ -606,12 +645,21 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         ctl.flag = atomicAdd(&p.wstate[row].parts_done, 1) == p.P - 1;
       }
       __syncthreads();
+#ifdef TLX_TIMELINE
+      if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 8] = global_timer_ns() - tl_t;
+#endif
       if (ctl.flag) {
         __threadfence();
         for (int i = threadIdx.x; i < kStWin; i += kStThreads) area[i] = __ldcg(gh + i);
         __syncthreads();
+#ifdef TLX_TIMELINE
+        if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 10] = global_timer_ns() - tl_t;
+#endif
         const int v = st_wide_threshold(p, row, key16, p.sp.top_p[row], area, ctl.wide);
-        if (threadIdx.x == 0) p.wstate[row].vstar16 = v;
+        if (threadIdx.x == 0) { p.wstate[row].kmax16 = ctl.wide.kmax16; p.wstate[row].vstar16 = v; }
+#ifdef TLX_TIMELINE
+        if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 11] = global_timer_ns() - tl_t;
+#endif
       }
     }
     __syncthreads();   // the producer's fifo entries are visible; the shared window is free again
@@ -680,31 +728,43 @@ __device__ __forceinline__ void tl_place(TailShared& t, const StreamParams& p, c
 // count * exp(value - max)), then the Gumbel arg-max over the kept candidates.  Returns the token, or
 // -1 if the lists cannot be trusted to hold the row's top-K or the keys spread over more than kTlBins
 // values (the caller then takes the whole-row routines).  All threads call; hist[] must be zero.
-static __device__ __noinline__ int st_finish_normal(const StreamParams& p, int row, const StreamDesc& d, float pp, float T_,
-                                                    TailShared& t) {
+// What a thread of a row CTA fetches of the row's candidate lists in the first round trip: thread =
+// (segment, half); the count of the segment and every second 16-byte vector of its first kStSpec entries.
+struct TailFetch {
+  uint4 e[4];
+  int cnt;
+};
+__device__ __forceinline__ TailFetch tl_fetch(const StreamParams& p, int row) {
+  constexpr int kSubs = kStSpec / 16;
+  const int nseg = p.P * kStWarps;
+  const int sg = (int)threadIdx.x / kSubs, sub = (int)threadIdx.x % kSubs;
+  TailFetch r;
+  r.cnt = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) r.e[q] = make_uint4(0, 0, 0, 0);
+  if (sg < nseg) {
+    r.cnt = __ldcg(p.counts + (size_t)row * nseg + sg);
+    const uint4* src = reinterpret_cast<const uint4*>(p.cands + ((size_t)row * nseg + sg) * kStWarpCap) + sub;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) r.e[q] = __ldcg(src + q * kSubs);
+  }
+  return r;
+}
+
+__device__ __forceinline__ int st_finish_normal(const StreamParams& p, int row, const StreamDesc& d, float pp, float T_,
+                                                    const TailFetch& fetched, TailShared& t) {
   const SampleParams& sp = p.sp;
   const int K = d.K;
   const int nseg = p.P * kStWarps;
   const int lane = lane_id(), warp = warp_id();
   const int64_t nrow = row + sp.dim0_offset;
   const float* noise_row = sp.noise.dense ? sp.noise.dense + nrow * sp.noise.stride : nullptr;
-  // ---- one round trip: every segment's count and its first kStSpec entries (16 per thread and round)
+  // ---- one round trip: every segment's count and its first kStSpec entries (thread = segment and half)
+  constexpr int kSubs = kStSpec / 16;   // threads per segment
   const uint32_t* cbase = p.cands + (size_t)row * nseg * kStWarpCap;
-  uint4 e[2][4];
-  int cnt[2];
-#pragma unroll
-  for (int it = 0; it < 2; ++it) {
-    const int pair = (int)threadIdx.x + it * kStThreads;
-    const int sg = pair >> 2, sub = pair & 3;
-    cnt[it] = 0;
-    if (sg < nseg) {
-      cnt[it] = __ldcg(p.counts + (size_t)row * nseg + sg);
-      const uint4* src = reinterpret_cast<const uint4*>(cbase + (size_t)sg * kStWarpCap + sub * 16);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) e[it][q] = __ldcg(src + q);
-      if (sub == 0) t.segcnt[sg] = cnt[it];
-    }
-  }
+  const int sg = (int)threadIdx.x / kSubs, sub = (int)threadIdx.x % kSubs;
+  const int cnt = fetched.cnt;
+  if (sg < nseg && sub == 0) t.segcnt[sg] = cnt;
   if (threadIdx.x == 0) { t.maxbin = 0; t.overflow = 0; t.nties = 0; }
   __syncthreads();
   // ---- the segments' offsets (warp 0: four segments per lane)
@@ -740,25 +800,22 @@ static __device__ __noinline__ int st_finish_normal(const StreamParams& p, int r
   // ---- candidates: tokens and keys to shared memory, keys into the histogram
   {
     int mymax = 0, over = 0;
-#pragma unroll
-    for (int it = 0; it < 2; ++it) {
-      const int pair = (int)threadIdx.x + it * kStThreads;
-      const int sg = pair >> 2, sub = pair & 3;
-      if (sg < nseg) {
-        const int f0 = t.segoff[sg];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t w4[4] = {e[it][q].x, e[it][q].y, e[it][q].z, e[it][q].w};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int idx = sub * 16 + q * 4 + k;
-            if (idx < cnt[it]) tl_place(t, p, d, noise_row, w4[k], sg, f0 + idx, mymax, over);
-          }
-        }
-        // what a segment holds beyond the entries fetched ahead (rare)
-        for (int idx = kStSpec + sub; idx < cnt[it]; idx += 4)
-          tl_place(t, p, d, noise_row, __ldcg(cbase + (size_t)sg * kStWarpCap + idx), sg, f0 + idx, mymax, over);
+    if (sg < nseg) {
+      const int f0 = t.segoff[sg];
+      // rolled on purpose (as are the loops below): this code runs once per CTA, so the time goes into
+      // fetching its instructions, not into executing them
+#pragma unroll 1
+      for (int i = 0; i < 16; ++i) {
+        const int q = i >> 2, k = i & 3;
+        const uint4 v = q == 0 ? fetched.e[0] : q == 1 ? fetched.e[1] : q == 2 ? fetched.e[2] : fetched.e[3];
+        const uint32_t w = k == 0 ? v.x : k == 1 ? v.y : k == 2 ? v.z : v.w;
+        const int idx = (sub + q * kSubs) * 4 + k;
+        if (idx >= cnt) break;
+        tl_place(t, p, d, noise_row, w, sg, f0 + idx, mymax, over);
       }
+      // what a segment holds beyond the entries fetched ahead
+      for (int idx = kStSpec + sub; idx < cnt; idx += kSubs)
+        tl_place(t, p, d, noise_row, __ldcg(cbase + (size_t)sg * kStWarpCap + idx), sg, f0 + idx, mymax, over);
     }
     mymax = __reduce_max_sync(0xFFFFFFFFu, mymax);
     if (lane == 0) atomicMax(&t.maxbin, mymax);
@@ -858,45 +915,52 @@ static __device__ __noinline__ int st_finish_normal(const StreamParams& p, int r
   const int vstar_idx = t.vstar_idx;
   const bool cut_ties = vstar_idx == vk_idx && admitted < ties_total;
   TLX_STAMP(sp, 5);
-  // the lowest tokens of the boundary group are the admitted ones: list the group's tokens
+  // the lowest tokens of the boundary group are the admitted ones: list the group's tokens, then mark
+  // (top bit of the token) the group's members beyond the admitted ones
   uint32_t* tie_tok = t.hist;   // the histogram is no longer needed
   if (cut_ties) {
     __syncthreads();
+#pragma unroll 1
     for (int f = threadIdx.x; f < m; f += kStThreads)
       if (kmax16 - (int)t.key[f] == vk_idx) tie_tok[atomicAdd(&t.nties, 1)] = t.tok[f];
     __syncthreads();
+    const int nties = t.nties;
+#pragma unroll 1
+    for (int f = threadIdx.x; f < m; f += kStThreads) {
+      if (kmax16 - (int)t.key[f] != vk_idx) continue;
+      const uint32_t tok = t.tok[f];
+      uint32_t rank = 0;
+#pragma unroll 1
+      for (int j = 0; j < nties; ++j) rank += tie_tok[j] < tok ? 1u : 0u;
+      if (rank >= (uint32_t)admitted) t.tok[f] = tok | 0x80000000u;
+    }
+    // each thread reads back only entries that it marked itself (same f stride below)
   }
-  const int nties = t.nties;
-  auto kept = [&](int f) {
-    const int idx = kmax16 - (int)t.key[f];
-    if (idx > vstar_idx) return false;
-    if (idx < vk_idx || !cut_ties) return true;
-    uint32_t rank = 0;
-    const uint32_t tk = t.tok[f];
-    for (int j = 0; j < nties; ++j) rank += tie_tok[j] < tk ? 1u : 0u;
-    return rank < (uint32_t)admitted;
-  };
-  // ---- Gumbel arg-max over the kept candidates, screened in f32
+  TLX_STAMP(sp, 10);
+  // ---- Gumbel arg-max over the kept candidates, screened in f32 (four loads in flight per thread)
   const float inv_T = 1.0f / T_;
+  const int kmin16 = kmax16 - vstar_idx;   // kept: key >= kmin16 and not marked
   float a1 = -INFINITY, a2 = -INFINITY, u1 = 0.5f;
   int f1 = -1, t1 = 0x7FFFFFFF;
 #pragma unroll 1
   for (int f0 = threadIdx.x; f0 < m; f0 += 4 * kStThreads) {
     float uu[4];
-    bool kk[4];
+    uint32_t tk[4];
+    int ky[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int f = f0 + u * kStThreads;
-      kk[u] = f < m && kept(f);
-      uu[u] = kk[u] ? sp.noise.at(nrow, (int64_t)t.tok[f]) : 0.5f;
+      tk[u] = f < m ? t.tok[f] : 0x80000000u;
+      ky[u] = f < m ? (int)t.key[f] : 0;
+      if (ky[u] < kmin16) tk[u] = 0x80000000u;
+      uu[u] = (tk[u] >> 31) ? 0.5f : sp.noise.at(nrow, (int64_t)tk[u]);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int f = f0 + u * kStThreads;
-      if (kk[u]) {
-        const float a = fmaf(key16_value(t.key[f]), inv_T, gumbel_screen(uu[u]));
-        const int tk = (int)t.tok[f];
-        if (a > a1 || (a == a1 && tk < t1)) { a2 = a1; a1 = a; u1 = uu[u]; f1 = f; t1 = tk; }
+      if (!(tk[u] >> 31)) {
+        const float a = fmaf(key16_value(ky[u]), inv_T, gumbel_screen(uu[u]));
+        const int tok = (int)tk[u];
+        if (a > a1 || (a == a1 && tok < t1)) { a2 = a1; a1 = a; u1 = uu[u]; f1 = f0 + u * kStThreads; t1 = tok; }
         else if (a > a2) a2 = a;
       }
     }
@@ -917,11 +981,13 @@ static __device__ __noinline__ int st_finish_normal(const StreamParams& p, int r
   if (!crowded) {
     if (f1 >= 0 && a1 >= cut) best = Best{__fdiv_rn(key16_value(t.key[f1]), T_) + gumbel_exact(u1), t1};
   } else {
+#pragma unroll 1
     for (int f = threadIdx.x; f < m; f += kStThreads) {
-      if (kept(f)) {
-        const float u = sp.noise.at(nrow, (int64_t)t.tok[f]);
+      const uint32_t tok = t.tok[f];
+      if ((int)t.key[f] >= kmin16 && !(tok >> 31)) {
+        const float u = sp.noise.at(nrow, (int64_t)tok);
         const float x = key16_value(t.key[f]);
-        if (fmaf(x, inv_T, gumbel_screen(u)) >= cut) best = best_of(best, Best{__fdiv_rn(x, T_) + gumbel_exact(u), (int)t.tok[f]});
+        if (fmaf(x, inv_T, gumbel_screen(u)) >= cut) best = best_of(best, Best{__fdiv_rn(x, T_) + gumbel_exact(u), (int)tok});
       }
     }
   }
@@ -929,86 +995,97 @@ static __device__ __noinline__ int st_finish_normal(const StreamParams& p, int r
   return btok;
 }
 
-// One row of the finish kernel's row CTAs.
-static __device__ __forceinline__ void st_finish_row(const StreamParams& p, int row, unsigned char* smem) {
-  TailShared& t = *reinterpret_cast<TailShared*>(smem);
+// One row of the finish kernel's row CTAs: normal rows are finished from their candidate lists; what that
+// cannot settle takes the whole-row routines.
+static __device__ __forceinline__ void st_finish_row(const StreamParams& p, int row, unsigned char* smem);
+
+// A row that the short paths left unanswered: exact whole-row routines (out of line: rare and slow, and
+// its stack frame and register needs stay out of the callers' way).  All threads call.
+static __device__ __noinline__ void st_slow_row(const StreamParams& p, int row, unsigned char* smem) {
+#ifdef TLX_SIZE_PROBE
+  return;
+#endif
   SelectShared& s = *reinterpret_cast<SelectShared*>(smem);
-  unsigned char* uni = smem + kSharedHeader;
-  uint64_t* cand = reinterpret_cast<uint64_t*>(uni);
-  uint32_t* win = reinterpret_cast<uint32_t*>(uni);
+  uint64_t* cand = reinterpret_cast<uint64_t*>(smem + kSharedHeader);
+  uint32_t* win = reinterpret_cast<uint32_t*>(smem + kSharedHeader);
   const SampleParams& sp = p.sp;
-  for (int i = threadIdx.x; i < kTlBins; i += kStThreads) t.hist[i] = 0;
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // the stream kernel's lists and thresholds are complete
   const StreamDesc d = p.desc[row];
   const int64_t n = sp.vocab;
   const __nv_bfloat16* rowp = reinterpret_cast<const __nv_bfloat16*>(sp.logits) + (int64_t)row * sp.row_stride;
   const float pp = sp.top_p[row], T_ = sp.temperature[row];
   const int64_t nrow = row + sp.dim0_offset;
   int status = 0, tok = 0;
-  bool have_token = true;
-  TLX_STAMP(sp, 0);
   __syncthreads();
   if (d.cls == kStNormal) {
     const int K = d.K;
-    TLX_STAMP(sp, 1);
-    tok = st_finish_normal(p, row, d, pp, T_, t);
-    if (tok < 0) {
-      // threshold too high for this row, a list overflowed, or keys too far apart: exact select, sorting tail
-      __syncthreads();
-      exact_select_row<TLX_BF16>(rowp, n, K, s, cand);
-      status |= kStatusRedone;
-      __syncthreads();
-      if (T_ < kSamplingEps) {
-        uint64_t best = 0;
-        for (int i = threadIdx.x; i < K; i += blockDim.x) {
-          const uint64_t c = ~cand[i];
-          best = c > best ? c : best;
-        }
-        block_max_u64(best, s);
-        tok = (int)cand_low(~best);
-      } else {
-        tok = tail_bf16_hist(sp, row, K, pp, T_, K, s, cand);
-        if (tok < 0) {
-          __syncthreads();
-          sort_candidates(cand, K);
-          tok = sample_tail<4>(
-              K, pp, T_, s, [&](int i) { return key_f32(cand_key(cand[i])); },
-              [&](int i) { return (int)cand_low(cand[i]); },
-              [&](int i) { return sp.noise.at(nrow, (int64_t)cand_low(cand[i])); });
-        }
+    status = kStatusRedone;
+    exact_select_row<TLX_BF16>(rowp, n, K, s, cand);
+    __syncthreads();
+    if (T_ < kSamplingEps) {
+      uint64_t best = 0;
+      for (int i = threadIdx.x; i < K; i += blockDim.x) {
+        const uint64_t c = ~cand[i];
+        best = c > best ? c : best;
+      }
+      block_max_u64(best, s);
+      tok = (int)cand_low(~best);
+    } else {
+      tok = tail_bf16_hist(sp, row, K, pp, T_, K, s, cand);
+      if (tok < 0) {
+        __syncthreads();
+        sort_candidates(cand, K);
+        tok = sample_tail<4>(
+            K, pp, T_, s, [&](int i) { return key_f32(cand_key(cand[i])); }, [&](int i) { return (int)cand_low(cand[i]); },
+            [&](int i) { return sp.noise.at(nrow, (int64_t)cand_low(cand[i])); });
       }
     }
-  } else if (d.cls == kStWide) {
-    status = kStatusGeneral;
-    if (__ldcg(&p.wstate[row].vstar16) >= 0) {
-      have_token = false;   // the final pass samples the row
-    } else {
-      RowPreset none;
-      tok = general_row_bf16<kWin>(rowp, n, (int)n, pp, T_, sp.noise, nrow, s, win, none);
-      status |= kStatusRedone;
-    }
   } else {
-    status = kStatusGeneral;
+    status = kStatusGeneral | (d.cls == kStWide ? (int)kStatusRedone : 0);
     int K = sp.top_k[row];
     if (K <= 0 || (int64_t)K >= n) K = (int)n;
     if (T_ < kSamplingEps) K = 1;
     if ((int64_t)K >= n && pp >= 1.0f) {
       tok = final_argmax<TLX_BF16>(rowp, n, T_, 0u, false, 0u, 0u, false, sp.noise, nrow, s);
     } else {
-      RowPreset pre;
-      tok = general_row_bf16<kWin>(rowp, n, K, pp, T_, sp.noise, nrow, s, win, pre);
+      RowPreset none;
+      tok = general_row_bf16<kWin>(rowp, n, K, pp, T_, sp.noise, nrow, s, win, none);
     }
+  }
+  if (threadIdx.x == 0) {
+    if (__ldcg(p.error_flag)) status |= kStatusTimeout;
+    sp.out_tokens[row] = tok;
+    if (sp.out_status) sp.out_status[row] = status;
+  }
+}
+
+static __device__ __forceinline__ void st_finish_row(const StreamParams& p, int row, unsigned char* smem) {
+  TailShared& t = *reinterpret_cast<TailShared*>(smem);
+  const SampleParams& sp = p.sp;
+  for (int i = threadIdx.x; i < kTlBins; i += kStThreads) t.hist[i] = 0;
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // the stream kernel's lists and thresholds are complete
+  // one round trip for everything the row's short path reads first (whatever the row's class turns out to be)
+  const StreamDesc d = p.desc[row];
+  const float pp = sp.top_p[row], T_ = sp.temperature[row];
+  const int timeout = __ldcg(p.error_flag) ? (int)kStatusTimeout : 0;
+  const TailFetch fetched = tl_fetch(p, row);
+  TLX_STAMP(sp, 0);
+  __syncthreads();
+  bool slow = d.cls == kStOther;
+  if (d.cls == kStNormal) {
+    TLX_STAMP(sp, 1);
+    const int tok = st_finish_normal(p, row, d, pp, T_, fetched, t);
+    slow = tok < 0;   // threshold too high for this row, a list overflowed, or keys too far apart
+    if (!slow && threadIdx.x == 0) {
+      sp.out_tokens[row] = tok;
+      if (sp.out_status) sp.out_status[row] = timeout;
+    }
+  } else if (d.cls == kStWide) {
+    slow = __ldcg(&p.wstate[row].vstar16) < 0;   // the window did not settle the threshold
+    if (!slow && threadIdx.x == 0 && sp.out_status) atomicOr(sp.out_status + row, (int)kStatusGeneral | timeout);
   }
   TLX_STAMP(sp, 8);
   if (threadIdx.x == 0 && sp.timeline) sp.timeline[(size_t)blockIdx.x * 16 + 9] = d.cls;
-  if (threadIdx.x == 0) {
-    if (__ldcg(p.error_flag)) status |= kStatusTimeout;
-    if (have_token) sp.out_tokens[row] = tok;
-    if (sp.out_status) {
-      if (have_token) sp.out_status[row] = status;
-      else atomicOr(sp.out_status + row, status);   // the final pass may be reporting a timeout for this row
-    }
-  }
+  if (slow) st_slow_row(p, row, smem);
 }
 
 // ---- finish: final pass over the wide rows ------------------------------------------------------------
@@ -1037,7 +1114,7 @@ __device__ __forceinline__ void fin_issue(const StreamParams& p, int row, int c,
 
 // Decides a wide row from the records of its ranges (all threads of the CTA that delivered the last one;
 // at most kStThreads records).
-static __device__ __noinline__ void fin_decide_row(const StreamParams& p, int row, int nrec, StControl& ctl) {
+__device__ __forceinline__ void fin_decide_row(const StreamParams& p, int row, int nrec, StControl& ctl) {
   const SampleParams& sp = p.sp;
   const FinRecord* recs = p.records + (size_t)row * p.nfin;
   const float T_ = sp.temperature[row];
@@ -1104,6 +1181,9 @@ static __device__ __noinline__ void fin_decide_row(const StreamParams& p, int ro
 // dense != 0: the noise is a tensor whose rows can be bulk-copied (16-byte aligned); it is streamed next
 // to the logits.  Otherwise the noise of the kept elements is read (or generated from the key) one by one.
 static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int dense, unsigned char* smem) {
+#ifdef TLX_SIZE_PROBE2
+  return;
+#endif
   unsigned char* ring = smem;
   StControl& ctl = *reinterpret_cast<StControl*>(smem + kFinSlots * kFinSlotBytes);
   int* wlist = reinterpret_cast<int*>(smem + kFinFixedSmem);
@@ -1155,6 +1235,7 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
     if (threadIdx.x == 0) {
       for (int s = 0; s < kFinSlots; ++s) mbar_init(&ctl.mbar[s], 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      ctl.best_key = f32_key(-INFINITY);
       for (int s = 0; s < kFinSlots; ++s) fin_issue(p, row, c_begin + s, c_end, dense != 0, ring, ctl.mbar, s);
     }
     __syncthreads();
@@ -1163,14 +1244,22 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
     int t1 = 0x7FFFFFFF;
     int slot = 0;
     uint32_t phase = 0;
+    // No element scores above (value of the row's maximum) / T + its own Gumbel term: once the CTA knows a
+    // score `cb`, an element whose noise u gives -log(-log u) < cb - xtop - margin cannot come within the
+    // screening slack of the best, and -log u <= 1 - u ... so the test is one comparison of 1 - u with
+    // eps = exp(-(cb - xtop - margin)) (1 - u >= 1 - exp(-eps') for the exact bound eps'; eps is looser).
+    const float xtop = key16_value(__ldcg(&ws->kmax16)) * inv_T;
+    float published = -INFINITY;
     for (int c = c_begin; c < c_end; ++c) {
+      const float cb = key_f32(ctl.best_key);
+      const float eps = expf(-(cb - 2.0f * (kGumbelSlack + 1e-5f * fabsf(cb)) - xtop)) * 1.000001f;
       const bool arrived = mbar_wait_suspended(&ctl.mbar[slot], phase);
       if (c == c_begin && unit == (int)blockIdx.x) TLX_STAMP(sp, 2);
       const unsigned char* buf = ring + (size_t)slot * kFinSlotBytes;
       const float* nbuf = reinterpret_cast<const float*>(buf + kFinChunk);
       const int nvec = (c == p.nfin - 1) ? last_nvec : kFinChunk / 16;
       if (!(p.debug & 2)) {
-#pragma unroll
+#pragma unroll 1
         for (int jv = 0; jv < kFinVecPerThread; ++jv) {
           const int v = (int)threadIdx.x + jv * kStThreads;
           if (v < nvec) {
@@ -1186,6 +1275,9 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
                 const float4 n1 = *reinterpret_cast<const float4*>(nbuf + v * 8 + 4);
                 un[0] = n0.x; un[1] = n0.y; un[2] = n0.z; un[3] = n0.w;
                 un[4] = n1.x; un[5] = n1.y; un[6] = n1.z; un[7] = n1.w;
+                const float umax = fmaxf(fmaxf(fmaxf(un[0], un[1]), fmaxf(un[2], un[3])),
+                                         fmaxf(fmaxf(un[4], un[5]), fmaxf(un[6], un[7])));
+                if (1.0f - umax > eps) continue;   // none of the eight can matter
               }
               float sc[8];
               float v1 = -INFINITY, v2 = -INFINITY;
@@ -1193,8 +1285,9 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
               for (int e = 0; e < 8; ++e) {
                 const uint32_t hi = (e & 1) ? (wd[e >> 1] & 0xFFFF0000u) : (wd[e >> 1] << 16);
                 const float xf = __uint_as_float(hi);
-                const bool keep = !(xf < tvf);
+                bool keep = !(xf < tvf);
                 if (!dense) un[e] = keep ? sp.noise.at(nrow, c * kFinChunkElems + v * 8 + e) : 0.5f;
+                keep = keep && 1.0f - un[e] <= eps;
                 sc[e] = keep ? fmaf(xf, inv_T, gumbel_screen(un[e])) : -INFINITY;
                 const float lo = fminf(v1, sc[e]);
                 v1 = fmaxf(v1, sc[e]);
@@ -1217,6 +1310,7 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
           }
         }
       }
+      if (a1 > published) { atomicMax(&ctl.best_key, f32_key(a1)); published = a1; }
       if (__syncthreads_or(!arrived)) {   // a copy never arrived: give up, the row's status says so
         if (threadIdx.x == 0 && sp.out_status) atomicOr(sp.out_status + row, (int)kStatusTimeout);
         return;
@@ -1264,10 +1358,10 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
   TLX_STAMP(sp, 5);
 }
 
+constexpr size_t kStFinishRowSmem =
+    sizeof(TailShared) > kSharedHeader + kUnionBytes ? sizeof(TailShared) : kSharedHeader + kUnionBytes;
 constexpr size_t kStFinishFixedSmem =
-    (sizeof(TailShared) > kSharedHeader + kUnionBytes ? sizeof(TailShared) : kSharedHeader + kUnionBytes) > kFinFixedSmem
-        ? (sizeof(TailShared) > kSharedHeader + kUnionBytes ? sizeof(TailShared) : kSharedHeader + kUnionBytes)
-        : kFinFixedSmem;   // + one int per row (the final pass's list of wide rows)
+    kStFinishRowSmem > kFinFixedSmem ? kStFinishRowSmem : kFinFixedSmem;   // + one int per row (the final pass's list)
 
 // Grid: p.fin_ctas CTAs of the final pass, then one CTA per row.
 __global__ void __launch_bounds__(kStThreads, 3) sample_finish_kernel(StreamParams p, int dense) {

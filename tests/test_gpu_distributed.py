@@ -1,5 +1,7 @@
 """Two-GPU run of the vocab-sharded sampler over NCCL (skipped with fewer than two GPUs)."""
+import datetime
 import os
+import queue
 import socket
 
 import numpy as np
@@ -23,7 +25,8 @@ def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         from tallax_b200 import sampling
         from tests.conftest import to_dev
@@ -50,12 +53,27 @@ def test_vocab_sharded_two_gpus(cuda):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    got = dict(q.get(timeout=300) for _ in range(world))
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.start()
+        got = {}
+        for _ in range(world):
+            try:
+                rank, toks = q.get(timeout=300)
+            except queue.Empty:
+                pytest.fail("a rank delivered no result: exit codes %r" % [p.exitcode for p in procs])
+            got[rank] = toks
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        # a rank that is still alive here is stuck (or its peer died): do not leave it behind
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+                if p.is_alive():
+                    p.kill()
     B, V = 64, 151936
     x, tk, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=4, dtype="bf16")
     exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
