@@ -48,6 +48,22 @@ const char* tlx_last_error(void);
  * benchmark count launches per call instead of assuming them). */
 unsigned long long tlx_kernel_launches(void);
 
+/* Optional.  Touches `device` once (so that no later call makes its first query of the device
+ * inside a stream capture) and, with TLX_INIT_SIDE_STREAM, creates the calling thread's helper
+ * stream and events on it and lets tlx_sample use them.  Without this call the library creates no
+ * CUDA stream or event of its own, ever.                                                       */
+#define TLX_INIT_SIDE_STREAM 1u
+int tlx_init(int device, unsigned flags);
+
+/* ---- device operands -------------------------------------------------------------------------
+ * A caller under a tracing compiler (an XLA custom call, a CUDA graph whose key changes between
+ * replays) has the PRNG key and the batch offset only as device buffers.  The *_dev entry points
+ * take them that way: key_dev points to the key's two uint32 words in device memory,
+ * dim0_offset_dev (nullable = 0) to an int32 scalar in device memory; both are read by the kernels
+ * when they run, never by the host.  Everything else is as in the entry point of the same name.
+ * They replace the traced operands `rng_key` and `dim0_offset` of tallax/_src/sampling.py:185-208,
+ * 246-252 and tallax/_src/sparse_random.py:43-94.                                               */
+
 /* ---- gather --------------------------------------------------------------------
  * out[b,j] = values[b, idx[b,j]] (axis 1) or out[i,b] = values[idx[i,b], b] (axis 0);
  * an index outside [0, extent) yields 0, as the reference does.
@@ -130,6 +146,10 @@ int tlx_top_k(void* stream, const void* x, int dtype, int64_t rows, int64_t n, i
 int tlx_sparse_random_uniform(void* stream, uint32_t key0, uint32_t key1, const int32_t* idx0,
                               const int32_t* idx1, int64_t count, int64_t dim1_size, float minval,
                               float maxval, float* out);
+/* The same with the key as a device operand (see "device operands" below). */
+int tlx_sparse_random_uniform_dev(void* stream, const uint32_t* key_dev, const int32_t* idx0,
+                                  const int32_t* idx1, int64_t count, int64_t dim1_size, float minval,
+                                  float maxval, float* out);
 
 /* ---- top-p mask ------------------------------------------------------------------
  * topk_logits, out: f32 [k, batch], column b sorted descending along axis 0; p: f32[batch].
@@ -148,6 +168,9 @@ int tlx_top_p_mask(void* stream, const float* topk_logits, const float* p, int k
 int tlx_gumbel_argmax(void* stream, const float* logits, const int32_t* idx0, const int32_t* idx1,
                       int64_t rows, int64_t cols, uint32_t key0, uint32_t key1, int64_t dim1_size,
                       int axis, int32_t* out_pos);
+int tlx_gumbel_argmax_dev(void* stream, const float* logits, const int32_t* idx0, const int32_t* idx1,
+                          int64_t rows, int64_t cols, const uint32_t* key_dev, int64_t dim1_size,
+                          int axis, int32_t* out_pos);
 
 /* ---- candidate-level sampler ---------------------------------------------------
  * topk_logits [rows, k] (F32 or BF16) sorted descending with masked positions equal to
@@ -162,6 +185,11 @@ int tlx_top_p_and_sample(void* stream, const void* topk_logits, int dtype, const
                          const float* noise, int64_t noise_stride, uint32_t key0, uint32_t key1,
                          int64_t vocab_size, double replace_val, int64_t dim0_offset,
                          int32_t* out_tokens);
+int tlx_top_p_and_sample_dev(void* stream, const void* topk_logits, int dtype, const int32_t* topk_idx,
+                             int64_t rows, int k, const float* top_p, const float* temperature,
+                             const float* noise, int64_t noise_stride, const uint32_t* key_dev,
+                             int64_t vocab_size, double replace_val, const int32_t* dim0_offset_dev,
+                             int32_t* out_tokens);
 
 /* ---- fused sampler -------------------------------------------------------------
  * logits [rows, vocab] (F32 or BF16, row stride in elements) -> token ids int32[rows]
@@ -170,9 +198,9 @@ int tlx_top_p_and_sample(void* stream, const void* topk_logits, int dtype, const
  * out_status (nullable, device int32[rows]): bit 0 = the row took a path for rows without
  * (or with a very large) top-k, bit 1 = a bounded wait gave up (result invalid), bit 2 = the
  * row needed a second pass (first threshold too high, or candidate list overflow).
- * For large bf16 batches part of the work runs on a stream owned by the library, forked from
- * `stream` and joined back to it inside the call: all of the call's work is ordered on `stream`
- * as seen by the caller.
+ * All of the call's work is ordered on `stream`.  Only after tlx_init(device,
+ * TLX_INIT_SIDE_STREAM) may part of it run on a stream owned by the library, forked from
+ * `stream` and joined back to it inside the call (also when a launch or an event call fails).
  * Replaces the whole of tallax/_src/sampling.py:331-343 (`sample`), i.e. the
  * top_dynamic_k kernel (top_k.py:482-506) followed by _top_p_and_sample.            */
 size_t tlx_sample_workspace_bytes(int64_t rows, int64_t vocab);
@@ -181,6 +209,11 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
                const float* temperature, const float* noise, int64_t noise_stride, uint32_t key0,
                uint32_t key1, int64_t dim0_offset, int32_t* out_tokens, int32_t* out_status,
                void* workspace, size_t workspace_bytes);
+int tlx_sample_dev(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab,
+                   int64_t row_stride, const int32_t* top_k, const float* top_p,
+                   const float* temperature, const float* noise, int64_t noise_stride,
+                   const uint32_t* key_dev, const int32_t* dim0_offset_dev, int32_t* out_tokens,
+                   int32_t* out_status, void* workspace, size_t workspace_bytes);
 
 /* ---- vocab-sharded sampler -----------------------------------------------------
  * Stage 1, on each shard: the shard's top-`k_cand` as (f32 value, GLOBAL token id =
@@ -201,6 +234,12 @@ int tlx_shard_candidates(void* stream, const void* logits, int dtype, int64_t ro
                          int64_t noise_stride, uint32_t key0, uint32_t key1, int64_t vocab_total,
                          int64_t dim0_offset, float* out_vals, int32_t* out_idx, float* out_noise,
                          void* workspace, size_t workspace_bytes);
+int tlx_shard_candidates_dev(void* stream, const void* logits, int dtype, int64_t rows,
+                             int64_t v_local, int64_t row_stride, int64_t col_offset, int k_cand,
+                             const float* noise, int64_t noise_stride, const uint32_t* key_dev,
+                             int64_t vocab_total, const int32_t* dim0_offset_dev, float* out_vals,
+                             int32_t* out_idx, float* out_noise, void* workspace,
+                             size_t workspace_bytes);
 int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* cand_idx,
                          const float* cand_noise, int64_t rows, int n_cand, int k_per_block,
                          int64_t block_stride, int64_t row_stride, const int32_t* top_k,

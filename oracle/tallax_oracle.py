@@ -430,7 +430,7 @@ def merge_and_sample(cand_vals, cand_idx, cand_noise, top_k_, top_p, temperature
     flags = np.zeros(B, dtype=bool)
     for b in range(B):
         order = np.lexsort((np.asarray(cand_idx)[b], -key[b]))
-        K = min(int(kk[b]), M)
+        K = M if kk[b] <= 0 or kk[b] > M else int(kk[b])   # top_k <= 0: disabled, as in `sample`
         out[b], flags[b] = _row_sample(v[b][order], np.asarray(cand_idx)[b][order].astype(np.int64),
                                        np.asarray(cand_noise)[b][order], top_p[b], temperature[b], K)
     return (out, flags) if return_flags else out

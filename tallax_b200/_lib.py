@@ -22,6 +22,7 @@ SIGNATURES = {
     "tlx_abi_version": (_i32, []),
     "tlx_last_error": (C.c_char_p, []),
     "tlx_kernel_launches": (C.c_ulonglong, []),
+    "tlx_init": (_i32, [_i32, _u32]),
     "tlx_take_along_axis": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32]),
     "tlx_cumsum": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32]),
     "tlx_argmax": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _vp]),
@@ -33,6 +34,14 @@ SIGNATURES = {
     "tlx_top_k": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _f64, _i32, _vp, _vp, _vp, _vp, _vp,
                          _vp, _sz]),
     "tlx_sparse_random_uniform": (_i32, [_vp, _u32, _u32, _vp, _vp, _i64, _i64, _f32, _f32, _vp]),
+    "tlx_sparse_random_uniform_dev": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _f32, _vp]),
+    "tlx_gumbel_argmax_dev": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i32, _vp]),
+    "tlx_top_p_and_sample_dev": (_i32, [_vp, _vp, _i32, _vp, _i64, _i32, _vp, _vp, _vp, _i64, _vp, _i64, _f64, _vp,
+                                        _vp]),
+    "tlx_sample_dev": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp,
+                              _sz]),
+    "tlx_shard_candidates_dev": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _i64, _vp,
+                                        _vp, _vp, _vp, _vp, _sz]),
     "tlx_top_p_mask": (_i32, [_vp, _vp, _vp, _i32, _i64, _f64, _vp]),
     "tlx_gumbel_argmax": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _u32, _u32, _i64, _i32, _vp]),
     "tlx_top_p_and_sample": (_i32, [_vp, _vp, _i32, _vp, _i64, _i32, _vp, _vp, _vp, _i64, _u32, _u32, _i64, _f64,

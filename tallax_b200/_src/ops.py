@@ -77,6 +77,31 @@ def key_pair(rng_key) -> tuple[int, int]:
     return int(rng_key[0]) & 0xFFFFFFFF, int(rng_key[1]) & 0xFFFFFFFF
 
 
+def key_operand(rng_key):
+    """A key that lives on the device (a CUDA tensor of two 32-bit words) is passed to the library as a
+    device operand, without a copy to the host; returns that tensor (uint32 view) or None."""
+    if isinstance(rng_key, torch.Tensor) and rng_key.is_cuda:
+        k = rng_key.detach().reshape(-1)
+        if k.numel() != 2 or k.element_size() != 4:
+            raise ValueError("a device rng_key must hold two 32-bit words")
+        return k.contiguous().view(torch.int32)
+    return None
+
+
+def _host_offset(dim0_offset, dev):
+    """A host batch offset for an entry point that takes it as a device operand (None when it is zero)."""
+    return None if int(dim0_offset) == 0 else torch.tensor([int(dim0_offset)], dtype=torch.int32, device=dev)
+
+
+def offset_operand(dim0_offset):
+    """A batch offset that lives on the device (a CUDA int32 scalar tensor) stays there; returns it or None."""
+    if isinstance(dim0_offset, torch.Tensor) and dim0_offset.is_cuda:
+        if dim0_offset.numel() != 1:
+            raise ValueError("a device dim0_offset must be a scalar")
+        return dim0_offset.detach().reshape(1).to(torch.int32)
+    return None
+
+
 # ---------------------------------------------------------------------------------------
 def take_along_axis(values: torch.Tensor, indices: torch.Tensor, axis: int) -> torch.Tensor:
     values, indices = _dev(values), _dev(indices)
@@ -152,8 +177,13 @@ def sparse_random_uniform(key, idx0: torch.Tensor, idx1: torch.Tensor, dim1_size
     idx0, idx1 = _dev(idx0).to(torch.int32), _dev(idx1).to(torch.int32)
     if idx0.shape != idx1.shape:
         raise ValueError("index arrays must have the same shape")
-    k0, k1 = key_pair(key)
     out = torch.empty(idx0.shape, dtype=torch.float32, device=idx0.device)
+    kd = key_operand(key)
+    if kd is not None:
+        check(_lib.load().tlx_sparse_random_uniform_dev(_stream(), _ptr(kd), _ptr(idx0), _ptr(idx1), idx0.numel(),
+                                                        int(dim1_size), float(minval), float(maxval), _ptr(out)))
+        return out
+    k0, k1 = key_pair(key)
     check(_lib.load().tlx_sparse_random_uniform(_stream(), k0, k1, _ptr(idx0), _ptr(idx1), idx0.numel(),
                                                 int(dim1_size), float(minval), float(maxval), _ptr(out)))
     return out
@@ -175,10 +205,15 @@ def gumbel_argmax(key, logits, idx0, idx1, dim1_size, axis):
     logits = _dev(logits).float()
     idx0, idx1 = _dev(idx0).to(torch.int32), _dev(idx1).to(torch.int32)
     rows, cols = logits.shape
-    k0, k1 = key_pair(key)
     pos = torch.empty(rows if axis == 1 else cols, dtype=torch.int32, device=logits.device)
-    check(_lib.load().tlx_gumbel_argmax(_stream(), _ptr(logits), _ptr(idx0), _ptr(idx1), rows, cols, k0, k1,
-                                        int(dim1_size), int(axis), _ptr(pos)))
+    kd = key_operand(key)
+    if kd is not None:
+        check(_lib.load().tlx_gumbel_argmax_dev(_stream(), _ptr(logits), _ptr(idx0), _ptr(idx1), rows, cols, _ptr(kd),
+                                                int(dim1_size), int(axis), _ptr(pos)))
+    else:
+        k0, k1 = key_pair(key)
+        check(_lib.load().tlx_gumbel_argmax(_stream(), _ptr(logits), _ptr(idx0), _ptr(idx1), rows, cols, k0, k1,
+                                            int(dim1_size), int(axis), _ptr(pos)))
     sel = pos.reshape(-1, 1) if axis == 1 else pos.reshape(1, -1)
     return [take_along_axis(i, sel, axis).reshape(-1) for i in (idx0, idx1)]
 
@@ -188,7 +223,6 @@ def top_p_and_sample(topk_logits, topk_idx, top_p, temperature, *, vocab_size, r
     topk_logits, topk_idx = _dev(topk_logits), _dev(topk_idx).to(torch.int32)
     rows, k = topk_logits.shape
     dev = topk_logits.device
-    k0, k1 = key_pair(rng_key)
     if noise is not None:
         noise = _dev(noise)
         if noise.dtype != torch.float32 or noise.ndim != 2:
@@ -196,6 +230,17 @@ def top_p_and_sample(topk_logits, topk_idx, top_p, temperature, *, vocab_size, r
     elif rng_key is None:
         raise ValueError("either rng_key or noise is required")
     out = torch.empty(rows, dtype=torch.int32, device=dev)
+    kd, od = key_operand(rng_key), offset_operand(dim0_offset)
+    if kd is not None or od is not None:
+        if kd is None and noise is None:
+            kd = torch.tensor(key_pair(rng_key), dtype=torch.int64, device=dev).to(torch.int32)
+        check(_lib.load().tlx_top_p_and_sample_dev(
+            _stream(), _ptr(topk_logits), dtype_code(topk_logits), _ptr(topk_idx), rows, k,
+            _ptr(_f32vec(top_p, rows, dev)), _ptr(_f32vec(temperature, rows, dev)), _ptr(noise),
+            noise.shape[1] if noise is not None else 0, _ptr(kd), int(vocab_size), float(replace_val),
+            _ptr(od if od is not None else _host_offset(dim0_offset, dev)), _ptr(out)))
+        return out
+    k0, k1 = key_pair(rng_key)
     check(_lib.load().tlx_top_p_and_sample(
         _stream(), _ptr(topk_logits), dtype_code(topk_logits), _ptr(topk_idx), rows, k, _ptr(_f32vec(top_p, rows, dev)),
         _ptr(_f32vec(temperature, rows, dev)), _ptr(noise), noise.shape[1] if noise is not None else 0, k0, k1,
@@ -222,7 +267,6 @@ def sample(logits, top_k_, top_p, temperature, *, rng_key=None, noise=None, dim0
         raise ValueError("Only 2D inputs supported")
     rows, vocab = logits.shape
     dev = logits.device
-    k0, k1 = key_pair(rng_key)
     if noise is not None:
         noise = _dev(noise)
         if noise.dtype != torch.float32 or noise.ndim != 2 or noise.shape[1] < vocab:
@@ -230,6 +274,19 @@ def sample(logits, top_k_, top_p, temperature, *, rng_key=None, noise=None, dim0
     elif rng_key is None:
         raise ValueError("either rng_key or noise is required")
     w = workspace if workspace is not None else SampleWorkspace(rows, vocab, dev)
+    kd, od = key_operand(rng_key), offset_operand(dim0_offset)
+    if kd is not None or od is not None:
+        # key and/or offset live on the device: they are handed over as device operands
+        if kd is None and noise is None:
+            kd = torch.tensor(key_pair(rng_key), dtype=torch.int64, device=dev).to(torch.int32)
+        check(_lib.load().tlx_sample_dev(
+            _stream(), _ptr(logits), dtype_code(logits), rows, vocab, vocab, _ptr(_i32vec(top_k_, rows, dev)),
+            _ptr(_f32vec(top_p, rows, dev)), _ptr(_f32vec(temperature, rows, dev)), _ptr(noise),
+            noise.shape[1] if noise is not None else 0, _ptr(kd),
+            _ptr(od if od is not None else _host_offset(dim0_offset, dev)), _ptr(w.tokens), _ptr(w.status),
+            _ptr(w.ws), w.ws.numel()))
+        return (w.tokens, w.status) if return_status else w.tokens
+    k0, k1 = key_pair(rng_key)
     check(_lib.load().tlx_sample(
         _stream(), _ptr(logits), dtype_code(logits), rows, vocab, vocab, _ptr(_i32vec(top_k_, rows, dev)),
         _ptr(_f32vec(top_p, rows, dev)), _ptr(_f32vec(temperature, rows, dev)), _ptr(noise),
@@ -247,13 +304,24 @@ def shard_candidates(logits_shard, col_offset: int, k_cand: int, *, noise_shard=
     logits_shard = _dev(logits_shard)
     rows, v_local = logits_shard.shape
     dev = logits_shard.device
-    k0, k1 = key_pair(rng_key)
     if noise_shard is not None:
         noise_shard = _dev(noise_shard)
     elif rng_key is None:
         raise ValueError("either rng_key or noise_shard is required")
     if out is None:
         out = torch.empty((3, rows, k_cand), dtype=torch.float32, device=dev)
+    kd, od = key_operand(rng_key), offset_operand(dim0_offset)
+    if kd is not None or od is not None:
+        if kd is None and noise_shard is None:
+            kd = torch.tensor(key_pair(rng_key), dtype=torch.int64, device=dev).to(torch.int32)
+        check(_lib.load().tlx_shard_candidates_dev(
+            _stream(), _ptr(logits_shard), dtype_code(logits_shard), rows, v_local, v_local, int(col_offset),
+            int(k_cand), _ptr(noise_shard), noise_shard.shape[1] if noise_shard is not None else 0, _ptr(kd),
+            int(vocab_total if vocab_total is not None else v_local),
+            _ptr(od if od is not None else _host_offset(dim0_offset, dev)), out[0].data_ptr(), out[1].data_ptr(),
+            out[2].data_ptr(), None, 0))
+        return out
+    k0, k1 = key_pair(rng_key)
     check(_lib.load().tlx_shard_candidates(
         _stream(), _ptr(logits_shard), dtype_code(logits_shard), rows, v_local, v_local, int(col_offset), int(k_cand),
         _ptr(noise_shard), noise_shard.shape[1] if noise_shard is not None else 0, k0, k1,

@@ -41,6 +41,7 @@
 // row is streamed again with a lower one; the exact multi-pass select is the last resort.
 // Routines that run once per row or less are kept out of line, which keeps the per-slice loops
 // small in the instruction cache.
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -1445,7 +1446,7 @@ __device__ __forceinline__ void score_tile_plain(const SampleParams& p, const Ge
   const uint4* vp = reinterpret_cast<const uint4*>(buf);
   const bool noise_vec = p.noise.dense && ((reinterpret_cast<uintptr_t>(p.noise.dense) & 15) == 0) &&
                          ((p.noise.stride & 3) == 0);
-  const float* nbase = p.noise.dense ? p.noise.dense + nrow * p.noise.stride : nullptr;
+  const float* nbase = p.noise.dense ? p.noise.dense_row(nrow) : nullptr;
   for (int i0 = threadIdx.x; i0 < nvec; i0 += kPair * (int)blockDim.x) {
     uint4 v[kPair];
     float4 nz[kPair][VEC / 4];
@@ -1841,10 +1842,12 @@ __global__ void __launch_bounds__(128) top_p_mask_kernel(const float* __restrict
 __global__ void __launch_bounds__(256) gumbel_argmax_kernel(const float* __restrict__ logits,
                                                             const int32_t* __restrict__ idx0,
                                                             const int32_t* __restrict__ idx1, int64_t rows,
-                                                            int64_t cols, uint32_t k0, uint32_t k1, int64_t dim1,
+                                                            int64_t cols, uint32_t k0, uint32_t k1,
+                                                            const uint32_t* __restrict__ key_dev, int64_t dim1,
                                                             int axis, int32_t* __restrict__ out) {
   __shared__ float sy[8];
   __shared__ int sp[8];
+  if (key_dev) { k0 = __ldg(key_dev); k1 = __ldg(key_dev + 1); }
   const int64_t line = blockIdx.x;                    // row (axis 1) or column (axis 0)
   const int64_t len = axis == 1 ? cols : rows;
   const int64_t step = axis == 1 ? 1 : cols;
@@ -1892,8 +1895,12 @@ struct SideStream {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
 };
-static SideStream* side_stream() {
+// Off unless tlx_init asked for it: a library call then creates no CUDA object of its own, which a
+// caller inside a stream capture or under a tracing compiler relies on.
+static std::atomic<int> g_side_stream_enabled{0};
+static SideStream* side_stream(bool create_only = false) {
   static thread_local SideStream cache[64];
+  if (!g_side_stream_enabled.load(std::memory_order_relaxed) && !create_only) return nullptr;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return nullptr;
@@ -2054,8 +2061,15 @@ static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* wor
   StreamParams p{};
   p.sp = sp;
   p.P = l.P; p.part_chunks = l.part_chunks; p.nchunks = l.nchunks; p.nfin = l.nfin; p.row_bytes = sp.vocab * 2;
-  // final-pass CTAs of the finish kernel: what three CTAs per SM leave beside one CTA per row
-  p.fin_ctas = 3 * sms - (int)sp.rows < sms ? sms : 3 * sms - (int)sp.rows;
+  // the noise tensor can be streamed next to the logits if its rows start on 16-byte boundaries
+  const int dense = sp.noise.dense && (reinterpret_cast<uintptr_t>(sp.noise.dense) & 15) == 0 && (sp.noise.stride & 3) == 0;
+  // Wide rows' arg-max over their kept elements: with such a noise tensor the stream kernel does it (final
+  // items, one record each; at most 128 per row); otherwise the finish kernel makes a final pass with the
+  // CTAs that three per SM leave beside one per row.
+  const int64_t fin_items = (sp.vocab + kStFinalElems - 1) / kStFinalElems;
+  const bool final_in_stream = dense && fin_items <= 128 && fin_items <= l.nfin && !getenv("TLX_FINAL_IN_FINISH");
+  p.fin_items = final_in_stream ? (int)fin_items : 0;
+  p.fin_ctas = final_in_stream ? 0 : (3 * sms - (int)sp.rows < sms ? sms : 3 * sms - (int)sp.rows);
   p.error_flag = (int*)ws;
   p.item_counter = (int*)ws + 1;
   p.desc = (StreamDesc*)(ws + l.off_desc);
@@ -2103,8 +2117,6 @@ static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* wor
   TLX_TIMELINE_KERNEL(1);
   if ((rc = launch_dependent(sample_stream_kernel, (unsigned)sgrid, kStThreads, st_smem, st, "sample (stream)", p)) != TLX_OK) return rc;
   if (stages < 3) return TLX_OK;
-  // the noise tensor can be streamed next to the logits if its rows start on 16-byte boundaries
-  const int dense = sp.noise.dense && (reinterpret_cast<uintptr_t>(sp.noise.dense) & 15) == 0 && (sp.noise.stride & 3) == 0;
   TLX_TIMELINE_KERNEL(2);
   return launch_dependent(sample_finish_kernel, (unsigned)(p.fin_ctas + sp.rows), kStThreads, fin_smem, st,
                           "sample (finish)", p, dense);
@@ -2124,11 +2136,21 @@ size_t tlx_sample_workspace_bytes(int64_t rows, int64_t vocab) {
   return sliced > streamed ? sliced : streamed;
 }
 
-int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab, int64_t row_stride,
-               const int32_t* top_k, const float* top_p, const float* temperature, const float* noise,
-               int64_t noise_stride, uint32_t key0, uint32_t key1, int64_t dim0_offset, int32_t* out_tokens,
-               int32_t* out_status, void* workspace, size_t workspace_bytes) {
+// Key and row offset of a call: host values or device operands (see NoiseSrc).
+struct CallOperands {
+  uint32_t key0 = 0, key1 = 0;
+  int64_t dim0_offset = 0;
+  const uint32_t* key_dev = nullptr;
+  const int32_t* dim0_offset_dev = nullptr;
+};
+
+static int sample_impl(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab, int64_t row_stride,
+                       const int32_t* top_k, const float* top_p, const float* temperature, const float* noise,
+                       int64_t noise_stride, const CallOperands& op, int32_t* out_tokens, int32_t* out_status,
+                       void* workspace, size_t workspace_bytes) {
   cudaStream_t st = (cudaStream_t)stream;
+  const uint32_t key0 = op.key0, key1 = op.key1;
+  const int64_t dim0_offset = op.dim0_offset;
   TLX_CHECK_ARG(rows >= 0 && vocab >= 1, "sample: bad extent");
   TLX_CHECK_ARG(vocab < (1ll << 31) && rows < (1ll << 31), "sample: extent too large");
   TLX_CHECK_ARG(row_stride >= vocab, "sample: row stride smaller than the row");
@@ -2152,6 +2174,7 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
   p.logits = logits; p.rows = rows; p.vocab = vocab; p.row_stride = row_stride;
   p.top_k = top_k; p.top_p = top_p; p.temperature = temperature;
   p.noise.dense = noise; p.noise.stride = noise_stride; p.noise.k0 = key0; p.noise.k1 = key1; p.noise.vocab = vocab;
+  p.noise.key_dev = op.key_dev; p.noise.row_offset_dev = op.dim0_offset_dev;
   p.dim0_offset = dim0_offset; p.out_tokens = out_tokens; p.out_status = out_status;
   p.S = l.S; p.chunk_elems = l.chunk_elems; p.nchunks = l.nchunks;
   p.div_magic = ((1ull << 40) + (unsigned long long)l.S - 1) / (unsigned long long)l.S;
@@ -2191,23 +2214,34 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
       clusters = clusters < 1 ? 1 : (clusters > rows ? rows : clusters);
       // The two kernels work on disjoint rows: the cluster kernel goes to a side stream forked
       // from the caller's stream and joined back to it, so that they share the GPU.
+      // (Only after tlx_init(device, TLX_INIT_SIDE_STREAM); otherwise both run on the caller's stream.)
       SideStream* side = side_stream();
       cudaStream_t wst = st;
       if (side && cudaEventRecord(side->fork, st) == cudaSuccess &&
           cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
         wst = side->stream;
       sample_wide_rows_kernel<<<(unsigned)(clusters * kWideCluster), kThreads, kWideSmem, wst>>>(p);
-      TLX_CHECK_LAUNCH("sample (wide rows)");
-      if (wst != st) {
-        cudaError_t je = cudaEventRecord(side->join, wst);
-        if (je != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaEventRecord: %s", cudaGetErrorString(je));
+      const cudaError_t wide_err = cudaGetLastError();
+      // whatever happens below, the caller's stream is joined to the side stream before this call returns
+      bool joined = wst == st;
+      if (!joined && cudaEventRecord(side->join, wst) == cudaSuccess) {
+        if (wide_err == cudaSuccess) {
+          p.wide_elsewhere = 1;
+          sample_rows_kernel<TLX_BF16><<<grid, kRowsKThreads, kRowsSmem, st>>>(p);
+        }
+        joined = cudaStreamWaitEvent(st, side->join, 0) == cudaSuccess;
+      } else if (joined && wide_err == cudaSuccess) {
+        p.wide_elsewhere = 1;
+        sample_rows_kernel<TLX_BF16><<<grid, kRowsKThreads, kRowsSmem, st>>>(p);
       }
-      p.wide_elsewhere = 1;
-      sample_rows_kernel<TLX_BF16><<<grid, kRowsKThreads, kRowsSmem, st>>>(p);
-      if (wst != st) {
-        cudaError_t je = cudaStreamWaitEvent(st, side->join, 0);
-        if (je != cudaSuccess) return set_error(TLX_ERR_CUDA, "sample: cudaStreamWaitEvent: %s", cudaGetErrorString(je));
+      if (!joined) {
+        // the events failed: wait for the side stream on the host, so that nothing of this call outlives it
+        cudaStreamSynchronize(side->stream);
+        cudaGetLastError();
+        return set_error(TLX_ERR_CUDA, "sample: could not join the side stream");
       }
+      if (wide_err != cudaSuccess)
+        return set_error(TLX_ERR_CUDA, "sample (wide rows): launch failed: %s", cudaGetErrorString(wide_err));
     } else if (dtype == TLX_BF16) {
       p.only_general = 1;
       p.have_records = 1;
@@ -2246,17 +2280,57 @@ int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_
   return TLX_OK;
 }
 
-int tlx_top_p_and_sample(void* stream, const void* topk_logits, int dtype, const int32_t* topk_idx, int64_t rows,
-                         int k, const float* top_p, const float* temperature, const float* noise,
-                         int64_t noise_stride, uint32_t key0, uint32_t key1, int64_t vocab_size, double replace_val,
-                         int64_t dim0_offset, int32_t* out_tokens) {
+int tlx_init(int device, unsigned flags) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+    return set_error(TLX_ERR_INVALID, "init: no CUDA device %d", device);
+  int prev = 0;
+  cudaGetDevice(&prev);
+  if (cudaSetDevice(device) != cudaSuccess) return set_error(TLX_ERR_CUDA, "init: cudaSetDevice(%d) failed", device);
+  device_sm_count();
+  int rc = TLX_OK;
+  if (flags & TLX_INIT_SIDE_STREAM) {
+    if (side_stream(true)) g_side_stream_enabled.store(1);
+    else rc = set_error(TLX_ERR_CUDA, "init: could not create the side stream");
+  }
+  cudaSetDevice(prev);
+  return rc;
+}
+
+int tlx_sample(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab, int64_t row_stride,
+               const int32_t* top_k, const float* top_p, const float* temperature, const float* noise,
+               int64_t noise_stride, uint32_t key0, uint32_t key1, int64_t dim0_offset, int32_t* out_tokens,
+               int32_t* out_status, void* workspace, size_t workspace_bytes) {
+  CallOperands op;
+  op.key0 = key0; op.key1 = key1; op.dim0_offset = dim0_offset;
+  return sample_impl(stream, logits, dtype, rows, vocab, row_stride, top_k, top_p, temperature, noise, noise_stride, op,
+                     out_tokens, out_status, workspace, workspace_bytes);
+}
+
+int tlx_sample_dev(void* stream, const void* logits, int dtype, int64_t rows, int64_t vocab, int64_t row_stride,
+                   const int32_t* top_k, const float* top_p, const float* temperature, const float* noise,
+                   int64_t noise_stride, const uint32_t* key_dev, const int32_t* dim0_offset_dev, int32_t* out_tokens,
+                   int32_t* out_status, void* workspace, size_t workspace_bytes) {
+  if (!noise && !key_dev) return set_error(TLX_ERR_INVALID, "sample: neither noise nor a key given");
+  CallOperands op;
+  op.key_dev = key_dev; op.dim0_offset_dev = dim0_offset_dev;
+  return sample_impl(stream, logits, dtype, rows, vocab, row_stride, top_k, top_p, temperature, noise, noise_stride, op,
+                     out_tokens, out_status, workspace, workspace_bytes);
+}
+
+static int top_p_and_sample_impl(void* stream, const void* topk_logits, int dtype, const int32_t* topk_idx, int64_t rows,
+                                 int k, const float* top_p, const float* temperature, const float* noise,
+                                 int64_t noise_stride, const CallOperands& op, int64_t vocab_size, double replace_val,
+                                 int32_t* out_tokens) {
+  const uint32_t key0 = op.key0, key1 = op.key1;
+  const int64_t dim0_offset = op.dim0_offset;
   cudaStream_t st = (cudaStream_t)stream;
   TLX_CHECK_ARG(rows >= 0 && k >= 1, "top_p_and_sample: bad extent");
   if (k > 1024) return set_error(TLX_ERR_UNSUPPORTED, "top_p_and_sample: k=%d exceeds 1024", k);
   TLX_CHECK_ARG(vocab_size >= 1, "top_p_and_sample: vocab_size must be positive");
   if (rows == 0) return TLX_OK;
   TLX_CHECK_ARG(topk_logits && topk_idx && top_p && temperature && out_tokens, "top_p_and_sample: null pointer");
-  NoiseSrc ns{noise, noise_stride, key0, key1, vocab_size};
+  NoiseSrc ns{noise, noise_stride, key0, key1, vocab_size, op.key_dev, op.dim0_offset_dev};
   if (dtype == TLX_F32) {
     top_p_and_sample_kernel<TLX_F32><<<(unsigned)rows, 256, 0, st>>>((const float*)topk_logits, topk_idx, k, top_p,
                                                                       temperature, ns, (float)replace_val, dim0_offset,
@@ -2272,6 +2346,27 @@ int tlx_top_p_and_sample(void* stream, const void* topk_logits, int dtype, const
   return TLX_OK;
 }
 
+int tlx_top_p_and_sample(void* stream, const void* topk_logits, int dtype, const int32_t* topk_idx, int64_t rows,
+                         int k, const float* top_p, const float* temperature, const float* noise,
+                         int64_t noise_stride, uint32_t key0, uint32_t key1, int64_t vocab_size, double replace_val,
+                         int64_t dim0_offset, int32_t* out_tokens) {
+  CallOperands op;
+  op.key0 = key0; op.key1 = key1; op.dim0_offset = dim0_offset;
+  return top_p_and_sample_impl(stream, topk_logits, dtype, topk_idx, rows, k, top_p, temperature, noise, noise_stride, op,
+                               vocab_size, replace_val, out_tokens);
+}
+
+int tlx_top_p_and_sample_dev(void* stream, const void* topk_logits, int dtype, const int32_t* topk_idx, int64_t rows,
+                             int k, const float* top_p, const float* temperature, const float* noise,
+                             int64_t noise_stride, const uint32_t* key_dev, int64_t vocab_size, double replace_val,
+                             const int32_t* dim0_offset_dev, int32_t* out_tokens) {
+  if (!noise && !key_dev) return set_error(TLX_ERR_INVALID, "top_p_and_sample: neither noise nor a key given");
+  CallOperands op;
+  op.key_dev = key_dev; op.dim0_offset_dev = dim0_offset_dev;
+  return top_p_and_sample_impl(stream, topk_logits, dtype, topk_idx, rows, k, top_p, temperature, noise, noise_stride, op,
+                               vocab_size, replace_val, out_tokens);
+}
+
 int tlx_top_p_mask(void* stream, const float* topk_logits, const float* p, int k, int64_t batch, double replace_val,
                    float* out) {
   cudaStream_t st = (cudaStream_t)stream;
@@ -2284,17 +2379,29 @@ int tlx_top_p_mask(void* stream, const float* topk_logits, const float* p, int k
   return TLX_OK;
 }
 
-int tlx_gumbel_argmax(void* stream, const float* logits, const int32_t* idx0, const int32_t* idx1, int64_t rows,
-                      int64_t cols, uint32_t key0, uint32_t key1, int64_t dim1_size, int axis, int32_t* out_pos) {
+static int gumbel_argmax_impl(void* stream, const float* logits, const int32_t* idx0, const int32_t* idx1, int64_t rows,
+                              int64_t cols, uint32_t key0, uint32_t key1, const uint32_t* key_dev, int64_t dim1_size,
+                              int axis, int32_t* out_pos) {
   cudaStream_t st = (cudaStream_t)stream;
   TLX_CHECK_ARG(axis == 0 || axis == 1, "gumbel_argmax: axis must be 0 or 1, got %d", axis);
   TLX_CHECK_ARG(rows > 0 && cols > 0 && dim1_size > 0, "gumbel_argmax: bad extent");
   TLX_CHECK_ARG(logits && idx0 && idx1 && out_pos, "gumbel_argmax: null pointer");
   const int64_t lines = axis == 1 ? rows : cols;
-  gumbel_argmax_kernel<<<(unsigned)lines, 256, 0, st>>>(logits, idx0, idx1, rows, cols, key0, key1, dim1_size, axis,
-                                                       out_pos);
+  gumbel_argmax_kernel<<<(unsigned)lines, 256, 0, st>>>(logits, idx0, idx1, rows, cols, key0, key1, key_dev, dim1_size,
+                                                       axis, out_pos);
   TLX_CHECK_LAUNCH("gumbel_argmax");
   return TLX_OK;
+}
+
+int tlx_gumbel_argmax(void* stream, const float* logits, const int32_t* idx0, const int32_t* idx1, int64_t rows,
+                      int64_t cols, uint32_t key0, uint32_t key1, int64_t dim1_size, int axis, int32_t* out_pos) {
+  return gumbel_argmax_impl(stream, logits, idx0, idx1, rows, cols, key0, key1, nullptr, dim1_size, axis, out_pos);
+}
+
+int tlx_gumbel_argmax_dev(void* stream, const float* logits, const int32_t* idx0, const int32_t* idx1, int64_t rows,
+                          int64_t cols, const uint32_t* key_dev, int64_t dim1_size, int axis, int32_t* out_pos) {
+  if (!key_dev) return set_error(TLX_ERR_INVALID, "gumbel_argmax: null key");
+  return gumbel_argmax_impl(stream, logits, idx0, idx1, rows, cols, 0u, 0u, key_dev, dim1_size, axis, out_pos);
 }
 
 int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* cand_idx, const float* cand_noise,

@@ -489,7 +489,7 @@ __device__ __forceinline__ int rw_dense_pass(const RowsParams& p, int64_t row, f
   RwControl& ctl = *sm.ctl;
   const unsigned char* rowp = reinterpret_cast<const unsigned char*>(sp.logits) + row * sp.row_stride * 2;
   const int64_t nrow = row + sp.dim0_offset;
-  const float* nrowp = sp.noise.dense + nrow * sp.noise.stride;
+  const float* nrowp = sp.noise.dense_row(nrow);
   const int ngroups = (int)((sp.vocab + kRwDenseElems - 1) / kRwDenseElems);
   const float inv_T = 1.0f / T_;
   auto issue = [&](int c, int g) {
@@ -684,7 +684,7 @@ __global__ void __launch_bounds__(kRwThreads, 2) sample_rows_stream_kernel(RowsP
       TLX_STAMP(sp, 2);
       if (ok && sp.noise.dense && T_ >= kSamplingEps) {
         // most of the candidates' noise is wanted two microseconds from now: start it on its way to L2
-        const float* nr = sp.noise.dense + nrow * sp.noise.stride;
+        const float* nr = sp.noise.dense_row(nrow);
         const int n = wc < kRwWarpCap ? wc : kRwWarpCap;
         for (int i = lane; i < n; i += 32) prefetch_l2(nr + wtok[i]);
       }

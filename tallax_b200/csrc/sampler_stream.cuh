@@ -59,6 +59,11 @@ constexpr int kStMinVocab = 16384;
 constexpr int kFinChunk = 8192;                      // final pass: bytes of logits per slot ...
 constexpr int kFinChunkElems = kFinChunk / 2;
 constexpr int kFinNoiseChunk = kFinChunkElems * 4;   // ... and of f32 noise
+// final items of the stream kernel: the logits and the noise of kStFinalElems elements of a wide row, in
+// chunks that fill a slot of the ring (2 + 4 bytes per element)
+constexpr int kStFinalChunkElems = kStChunk / 6;
+constexpr int kStFinalChunks = 4;
+constexpr int kStFinalElems = kStFinalChunks * kStFinalChunkElems;
 constexpr int kFinSlots = 2;
 constexpr int kFinVecPerThread = kFinChunk / 16 / kStThreads;   // 2
 static_assert(kStMaxPartChunks * kStChunkElems <= 65536, "candidate positions are 16 bits");
@@ -75,12 +80,20 @@ struct __align__(16) StreamDesc {
 };
 
 struct __align__(16) WideState {
-  int vstar16;               // kept: value >= the value of this key; -1: the window did not settle the threshold
+  int result;                // kWideNotReady until the row's threshold is settled; then -1 (the window did not
+                             // settle it) or (key of the greatest element - threshold key) << 16 | threshold key:
+                             // an element is kept if its value is not below the value of the threshold key
   int parts_done;            // stream kernel: parts of the row whose totals are in
-  int done;                  // final pass: ranges that have delivered their record
-  int kmax16;                // key of the row's greatest element (valid with vstar16 >= 0)
+  int done;                  // final pass of the finish kernel: ranges that have delivered their record
+  uint32_t best_key;         // final items of the stream kernel: best screened score of the row so far (ordered key)
 };
 static_assert(sizeof(WideState) == 16, "WideState layout");
+constexpr int kWideNotReady = (int)0x80000000;
+__device__ __forceinline__ int wide_result(int kmax16, int vstar16) {
+  return vstar16 < 0 ? -1 : ((kmax16 - vstar16) << 16) | vstar16;
+}
+__device__ __forceinline__ int wide_vstar16(int result) { return result < 0 ? -1 : (result & 0xFFFF); }
+__device__ __forceinline__ int wide_kmax16(int result) { return (result & 0xFFFF) + (result >> 16); }
 
 struct __align__(16) FinRecord {   // best element of one range of chunks of a wide row
   float a;          // its screened score
@@ -105,6 +118,8 @@ struct StreamParams {
   int* wflag;            // [rows] wide rows: an element lay above the window
   WideState* wstate;     // [rows]
   FinRecord* records;    // [rows * nfin]
+  int fin_items;             // final items per wide row (kStFinalElems elements each); 0: the finish
+                             // kernel makes the final pass over the wide rows
   int* item_counter;     // [1] next unclaimed item - gridDim.x (cleared by the prologue)
   int* error_flag;       // [1] a bounded wait of the stream kernel gave up (cleared by the prologue)
   int debug;             // diagnostic switches, 0 in normal use
@@ -156,6 +171,8 @@ struct __align__(16) StControl {
   int flag;
   int vstar;
   uint32_t best_key;      // final pass: the CTA's best screened score so far, as an ordered key
+  int fin_result;         // final item: the row's WideState::result
+  float fin_T;            // ... and temperature
   double dsum[kStWarps];
   double dlump[kStWarps];
   uint32_t wkey[kStWarps];
@@ -250,6 +267,23 @@ static __device__ __forceinline__ int st_wide_threshold(const StreamParams& p, i
   return wide_threshold_core<kStThreads>(wtop, pp, hist, lump, bad, ws);
 }
 
+// A row's class as far as its parameters decide it (the prologue may still turn a row into kStOther on
+// what it finds in the row's sample).  K_out: the effective top-k.
+__device__ __forceinline__ int st_param_class(int top_k, float pp, float T_, int64_t V, int& K_out) {
+  int K = top_k;
+  if (K <= 0 || (int64_t)K >= V) K = (int)V;
+  if (T_ < kSamplingEps) K = 1;   // greedy: the top candidate
+  K_out = K;
+  if (K <= kStMaxK) {
+    // rank in the sample that leaves, with four standard deviations of margin, at least K elements of the
+    // row at or above the sample's element of that rank: too many candidates -> whole-row routines
+    const float mu = (float)K * (float)kStSample / (float)V;
+    const int r = (int)(mu + 4.0f * sqrtf(mu) + 2.999f);
+    return (float)r * (float)V / (float)kStSample > 0.8f * (float)kMergeCap ? kStOther : kStNormal;
+  }
+  return ((int64_t)K >= V && pp < 1.0f) ? kStWide : kStOther;
+}
+
 // ---- prologue ----------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamParams p) {
   __shared__ int red[2][kStProThreads / 32];
@@ -270,15 +304,10 @@ __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamPa
     const int64_t start = ((int64_t)g * (nv - 32)) / (kStSampleVecs * (kStProThreads / 32) - 1);
     sv[j] = __ldg(vp + start + lane);
   }
-  int K = p.sp.top_k[row];
   const float T_ = p.sp.temperature[row];
   const float pp = p.sp.top_p[row];
-  if (K <= 0 || (int64_t)K >= V) K = (int)V;
-  if (T_ < kSamplingEps) K = 1;   // greedy: the top candidate
-  int cls;
-  if (K <= kStMaxK) cls = kStNormal;
-  else if ((int64_t)K >= V && pp < 1.0f) cls = kStWide;
-  else cls = kStOther;
+  int K;
+  int cls = st_param_class(p.sp.top_k[row], pp, T_, V, K);
 
   __nv_bfloat162 h[kStSampleVecs * 4];
 #pragma unroll
@@ -293,7 +322,6 @@ __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamPa
     // of the row at or above the sample's element of that rank
     const float mu = (float)K * (float)kStSample / (float)V;
     int r = (int)(mu + 4.0f * sqrtf(mu) + 2.999f);
-    if ((float)r * (float)V / (float)kStSample > 0.8f * (float)kMergeCap) cls = kStOther;   // too many candidates
     r = r > kStSample ? kStSample : r;
     // largest key t (not a NaN key) with #(sample >= t) >= r: sixteen halvings, counted with packed compares
     int lo = 0, hi = 0xFF81;
@@ -328,6 +356,11 @@ __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamPa
     for (int w = 0; w < kStProThreads / 32; ++w) km = max(km, red[0][w]);
     if (km > 0xFF80) {
       cls = kStOther;   // a NaN in the sample: the whole-row routines know what to do
+      if (threadIdx.x == 0) {   // the stream kernel lists the row by its parameters: its final items see "unsettled"
+        WideState ws{};
+        ws.result = -1;
+        p.wstate[row] = ws;
+      }
     } else {
       key16 = min(km + kStWinExtra, 0xFF80);
       xref = key16_value(key16);
@@ -336,6 +369,8 @@ __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamPa
       if (threadIdx.x == 0) {
         p.wflag[row] = 0;
         WideState ws{};
+        ws.result = kWideNotReady;
+        ws.best_key = f32_key(-INFINITY);
         p.wstate[row] = ws;
       }
     }
@@ -438,18 +473,26 @@ __device__ __forceinline__ void st_hist_chunk(const unsigned char* buf, int nvec
 // wide rows (they take longest) early, but only every third item, so that an SM rarely works on several
 // of them at a time; rows of class "other" are not streamed.
 struct StProducer {
-  int item;    // >= 0: there is an item; -1: no more
-  int row, part, chunk;
+  int item;    // >= 0: there is an item (its code); -1: no more
+  int row, part, chunk, nchunks;
   int next;    // claimed index (0, 1, ... among the claimed items)
   int pushed;
 };
 
+// Item codes: row << 8 | part for the logits of a part of a row; row << 8 | 0x80 | sub for a final item
+// (logits and noise of the elements [sub * kStFinalElems, (sub + 1) * kStFinalElems) of a wide row).
 struct StOrder {
-  const unsigned short* rows;   // the wide rows behind the first wave, then the normal ones
-  int nwide_items, nnormal_items;
-  // claimed index -> row << 8 | part, or -1 past the end
-  __device__ __forceinline__ int item(int j, int P) const {
-    if (j >= nwide_items + nnormal_items) return -1;
+  const unsigned short* rows;   // all wide rows, then the normal rows behind the first wave
+  int nwide_all, nwide_first;   // wide rows; those of them inside the first wave (the list's first entries)
+  int nwide_items, nnormal_items, nfinal_items;
+  // claimed index -> code, or -1 past the end
+  __device__ __forceinline__ int item(int j, int P, int fin_items) const {
+    if (j >= nwide_items + nnormal_items) {
+      j -= nwide_items + nnormal_items;
+      if (j >= nfinal_items) return -1;
+      const int w = j / fin_items;
+      return ((int)rows[w] << 8) | 0x80 | (j - w * fin_items);
+    }
     int idx;   // index into the wide items (< nwide_items) or nwide_items + index into the normal items
     if (nnormal_items >= 2 * nwide_items) {
       if (j < 3 * nwide_items) idx = j % 3 == 0 ? j / 3 : nwide_items + (j - j / 3 - 1);
@@ -457,8 +500,13 @@ struct StOrder {
     } else {
       idx = j;   // too few normal items to spread the wide ones: wide first
     }
-    const int r = idx / P;   // both lists hold whole rows, the wide rows' entries come first
-    return ((int)rows[r] << 8) | (idx - r * P);
+    if (idx < nwide_items) {
+      const int r = idx / P;
+      return ((int)rows[nwide_first + r] << 8) | (idx - r * P);
+    }
+    idx -= nwide_items;
+    const int r = idx / P;
+    return ((int)rows[nwide_all + r] << 8) | (idx - r * P);
   }
 };
 
@@ -466,15 +514,38 @@ __device__ __forceinline__ int st_part_chunks(const StreamParams& p, int part) {
   const int rest = p.nchunks - part * p.part_chunks;
   return rest < p.part_chunks ? rest : p.part_chunks;
 }
+__device__ __forceinline__ int st_final_item_chunks(const StreamParams& p, int sub) {
+  const int64_t rest = p.sp.vocab - (int64_t)sub * kStFinalElems;
+  return rest >= kStFinalElems ? kStFinalChunks : (int)((rest + kStFinalChunkElems - 1) / kStFinalChunkElems);
+}
+__device__ __forceinline__ int st_code_chunks(const StreamParams& p, int code) {
+  return (code & 0x80) ? st_final_item_chunks(p, code & 0x7F) : st_part_chunks(p, code & 0x7F);
+}
 
 __device__ __forceinline__ void st_issue_chunk(const StreamParams& p, StProducer& ps, unsigned char* ring, StControl& ctl,
                                                int slot) {
-  const int c = ps.part * p.part_chunks + ps.chunk;
-  const int64_t off = (int64_t)c * kStChunk;
-  const int64_t rest = p.row_bytes - off;
-  const uint32_t bytes = (uint32_t)(rest < kStChunk ? rest : kStChunk);
-  const unsigned char* src =
-      reinterpret_cast<const unsigned char*>(p.sp.logits) + (int64_t)ps.row * p.sp.row_stride * 2 + off;
+  const unsigned char* src;
+  uint32_t bytes;
+  if (ps.part & 0x80) {
+    // logits to the front of the slot, noise behind them
+    const int64_t e0 = (int64_t)(ps.part & 0x7F) * kStFinalElems + (int64_t)ps.chunk * kStFinalChunkElems;
+    const int64_t rest = p.sp.vocab - e0;
+    const uint32_t elems = (uint32_t)(rest < kStFinalChunkElems ? rest : kStFinalChunkElems);
+    unsigned char* dst = ring + (size_t)slot * kStChunk;
+    mbar_expect_tx(&ctl.mbar[slot], elems * 6);
+    bulk_load(dst, reinterpret_cast<const __nv_bfloat16*>(p.sp.logits) + (int64_t)ps.row * p.sp.row_stride + e0, elems * 2,
+              &ctl.mbar[slot]);
+    bulk_load(dst + kStFinalChunkElems * 2, p.sp.noise.dense_row(ps.row + p.sp.dim0_offset) + e0,
+              elems * 4, &ctl.mbar[slot]);
+    ps.chunk++;
+    return;
+  } else {
+    const int c = ps.part * p.part_chunks + ps.chunk;
+    const int64_t off = (int64_t)c * kStChunk;
+    const int64_t rest = p.row_bytes - off;
+    bytes = (uint32_t)(rest < kStChunk ? rest : kStChunk);
+    src = reinterpret_cast<const unsigned char*>(p.sp.logits) + (int64_t)ps.row * p.sp.row_stride * 2 + off;
+  }
   mbar_expect_tx(&ctl.mbar[slot], bytes);
   bulk_load(ring + (size_t)slot * kStChunk, src, bytes, &ctl.mbar[slot]);
   ps.chunk++;
@@ -485,19 +556,53 @@ __device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, 
                                          StControl& ctl, int slot) {
   for (;;) {
     if (ps.item < 0) return;
-    if (ps.chunk < st_part_chunks(p, ps.part)) break;
-    const int code = order.item(ps.next, p.P);
+    if (ps.chunk < ps.nchunks) break;
+    const int code = order.item(ps.next, p.P, p.fin_items);
     ps.item = code;
     if (code >= 0) {
       ps.row = code >> 8;
       ps.part = code & 0xFF;
       ps.chunk = 0;
+      ps.nchunks = st_code_chunks(p, code);
       ps.next = atomicAdd(p.item_counter, 1);
     }
     ctl.fifo[ps.pushed & 7] = code;
     ps.pushed++;
   }
   st_issue_chunk(p, ps, ring, ctl, slot);
+}
+
+// A chunk of a final item: logits (front of the slot) and noise (behind them) of the elements [elem0,
+// elem0 + 8 ngroups) of a wide row; a thread takes one group of eight.  Kept elements (value not below
+// tvf) whose noise passes the test 1 - u <= eps (see the main loop) are scored.
+// Per thread: the best two screened scores of the item so far (a1 >= a2), with the best one's noise, bf16
+// bits and token.
+__device__ __forceinline__ void st_final_chunk(const unsigned char* buf, int ngroups, int elem0, __nv_bfloat162 tv2,
+                                               float tvf, float inv_T, float eps, float& a1, float& a2, float& u1,
+                                               uint32_t& b1, int& t1) {
+  const int v = (int)threadIdx.x;
+  if (v >= ngroups) return;
+  const uint4 x = *reinterpret_cast<const uint4*>(buf + (size_t)v * 16);
+  const __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(bf162_bits(x.x), bf162_bits(x.y)), __hmax2_nan(bf162_bits(x.z), bf162_bits(x.w)));
+  if (__hblt2(m, tv2)) return;   // all eight below the threshold
+  const float* nbuf = reinterpret_cast<const float*>(buf + kStFinalChunkElems * 2) + v * 8;
+  const float4 n0 = *reinterpret_cast<const float4*>(nbuf);
+  const float4 n1 = *reinterpret_cast<const float4*>(nbuf + 4);
+  const float umax = fmaxf(fmaxf(fmaxf(n0.x, n0.y), fmaxf(n0.z, n0.w)), fmaxf(fmaxf(n1.x, n1.y), fmaxf(n1.z, n1.w)));
+  if (1.0f - umax > eps) return;   // none of the eight can matter
+  const unsigned short* xb = reinterpret_cast<const unsigned short*>(buf) + v * 8;
+#pragma unroll 1
+  for (int e = 0; e < 8; ++e) {
+    const float u = nbuf[e];
+    const uint32_t bits = xb[e];
+    const float xf = __uint_as_float(bits << 16);
+    if (!(xf < tvf) && 1.0f - u <= eps) {
+      const float a = fmaf(xf, inv_T, gumbel_screen(u));
+      const int tok = elem0 + v * 8 + e;
+      if (a > a1 || (a == a1 && tok < t1)) { a2 = a1; a1 = a; u1 = u; b1 = bits; t1 = tok; }
+      else if (a > a2) a2 = a;
+    }
+  }
 }
 
 // Shared memory beyond the fixed part: per row 4 bytes of descriptor (class << 16 | key) and 2 bytes of order.
@@ -522,40 +627,43 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   ps.row = (int)(blockIdx.x / (unsigned)p.P);
   ps.part = (int)(blockIdx.x % (unsigned)p.P);
   ps.chunk = 0;
+  ps.nchunks = st_part_chunks(p, ps.part);
   ps.next = 0;
   ps.pushed = 1;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStSlots; ++s) mbar_init(&ctl.mbar[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     ctl.fifo[0] = (ps.row << 8) | ps.part;
-    const int nc0 = st_part_chunks(p, ps.part);
-    for (int s = 0; s < kStSlots && s < nc0; ++s) st_issue_chunk(p, ps, ring, ctl, s);
+    for (int s = 0; s < kStSlots && s < ps.nchunks; ++s) st_issue_chunk(p, ps, ring, ctl, s);
   }
-  // everything below reads what the prologue kernel wrote
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  TLX_STAMP(p.sp, 6);
-  if (threadIdx.x == 0) ps.next = atomicAdd(p.item_counter, 1);   // used after the lists below are built
+  // The list of rows behind the first wave needs the rows' classes only as far as the parameters decide
+  // them (a row that the prologue downgrades is dropped when its items come up): it is built while the
+  // prologue kernel still runs.  All wide rows in row order (those of the first wave come first), then
+  // the normal rows behind the first wave.
+  uint32_t* pcls = dtab;   // parameter classes, replaced by the descriptors below
   for (int r = threadIdx.x; r < rows; r += kStThreads) {
-    const StreamDesc d = p.desc[r];
-    dtab[r] = ((uint32_t)d.cls << 16) | (uint32_t)d.key16;
+    int K;
+    pcls[r] = (uint32_t)st_param_class(p.sp.top_k[r], p.sp.top_p[r], p.sp.temperature[r], p.sp.vocab, K);
   }
   __syncthreads();
-  TLX_STAMP(p.sp, 7);
-  // the rows behind the first wave: the wide ones to the front of the list, the normal ones behind them
-  int nlisted = 0, nwide = 0;
+  int nlisted = 0, nwide = 0, nwide_first = 0;
+#pragma unroll 1
   for (int pass = 0; pass < 2; ++pass) {
     const uint32_t want = pass == 0 ? (uint32_t)kStWide : (uint32_t)kStNormal;
-    for (int base = first_rows; base < rows; base += kStThreads) {
+#pragma unroll 1
+    for (int base = pass == 0 ? 0 : first_rows; base < rows; base += kStThreads) {
       const int r = base + (int)threadIdx.x;
-      const bool take = r < rows && (dtab[r] >> 16) == want;
+      const bool take = r < rows && pcls[r] == want;
       const uint32_t mask = __ballot_sync(0xFFFFFFFFu, take);
-      if (lane == 0) ctl.ibest[warp] = __popc(mask);
+      const uint32_t early = __ballot_sync(0xFFFFFFFFu, take && r < first_rows);
+      if (lane == 0) { ctl.ibest[warp] = __popc(mask); ctl.wtok[warp] = __popc(early); }
       __syncthreads();
       int off = nlisted, total = 0;
-#pragma unroll
+#pragma unroll 1
       for (int w = 0; w < kStWarps; ++w) {
         if (w < warp) off += ctl.ibest[w];
         total += ctl.ibest[w];
+        if (pass == 0) nwide_first += ctl.wtok[w];
       }
       if (take) order_rows[off + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)r;
       nlisted += total;
@@ -563,10 +671,23 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
     }
     if (pass == 0) nwide = nlisted;
   }
+  // everything below reads what the prologue kernel wrote
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  TLX_STAMP(p.sp, 6);
+  if (threadIdx.x == 0) ps.next = atomicAdd(p.item_counter, 1);
+  for (int r = threadIdx.x; r < rows; r += kStThreads) {
+    const StreamDesc d = p.desc[r];
+    dtab[r] = ((uint32_t)d.cls << 16) | (uint32_t)d.key16;
+  }
+  __syncthreads();
+  TLX_STAMP(p.sp, 7);
   StOrder order;
   order.rows = order_rows;
-  order.nwide_items = nwide * p.P;
+  order.nwide_all = nwide;
+  order.nwide_first = nwide_first;
+  order.nwide_items = (nwide - nwide_first) * p.P;
   order.nnormal_items = (nlisted - nwide) * p.P;
+  order.nfinal_items = nwide * p.fin_items;
   if (threadIdx.x == 0) {
     // a first item shorter than the ring: go on into the claimed items
     for (int s = ps.chunk; s < kStSlots; ++s) st_issue(p, ps, order, ring, ctl, s);
@@ -580,7 +701,88 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   TLX_STAMP(p.sp, 1);
   for (int code = ctl.fifo[0]; code >= 0; code = ctl.fifo[taken & 7]) {
     ++taken;
-    const int row = code >> 8, part = code & 0xFF;
+    const int row = code >> 8, part = code & 0x7F;
+    if (code & 0x80) {
+      // ---- a final item: the Gumbel arg-max over the kept elements of a range of a wide row
+      if (threadIdx.x == 0) {
+        // the row's threshold: settled by whoever brought the last part of its histogram.  Those items were
+        // all claimed before this one, by CTAs that wait for nothing but their copies, so the wait is
+        // short; it is bounded all the same.
+        volatile int* rp = &p.wstate[row].result;
+        int res = *rp;
+        for (int spin = 0; res == kWideNotReady && spin < (1 << 16); ++spin) {
+          __nanosleep(64);
+          res = *rp;
+        }
+        if (res == kWideNotReady) { *p.error_flag = 1; res = -1; }
+        ctl.fin_result = res;
+        ctl.best_key = *reinterpret_cast<volatile uint32_t*>(&p.wstate[row].best_key);
+        ctl.fin_T = p.sp.temperature[row];
+      }
+      __syncthreads();
+      const int res = ctl.fin_result;
+      const float inv_T = 1.0f / ctl.fin_T;
+      const uint32_t tbits = key16_bf16_bits((uint32_t)wide_vstar16(res));
+      const __nv_bfloat162 tv2 = bf162_splat_bits(tbits);
+      const float tvf = __uint_as_float(tbits << 16);
+      const float xtop = key16_value(wide_kmax16(res)) * inv_T;
+      const int nc = st_final_item_chunks(p, part);
+      const int64_t last_elems = p.sp.vocab - ((int64_t)part * kStFinalElems + (int64_t)(nc - 1) * kStFinalChunkElems);
+      float a1 = -INFINITY, a2 = -INFINITY, u1 = 0.5f, published = -INFINITY;
+      uint32_t b1 = 0;
+      int t1 = 0x7FFFFFFF;
+      for (int ci = 0; ci < nc; ++ci) {
+        // No element scores above (value of the row's maximum) / T + its own Gumbel term g = -log(-log u),
+        // and -log u >= 1 - u: with cb a score that some kept element of the row reaches, an element
+        // with 1 - u > eps = exp(-(cb - xtop - margin)) has g < cb - xtop - margin.
+        const float cb = key_f32(ctl.best_key);
+        const float eps = expf(-(cb - 2.0f * (kGumbelSlack + 1e-5f * fabsf(cb)) - xtop)) * 1.000001f;
+        const bool arrived = mbar_wait_suspended(&ctl.mbar[slot], phase);
+        const unsigned char* buf = ring + (size_t)slot * kStChunk;
+        const int elem0 = part * kStFinalElems + ci * kStFinalChunkElems;
+        if (res >= 0 && !(p.debug & 1)) {
+          const int ngroups = ci != nc - 1 || last_elems >= kStFinalChunkElems ? kStFinalChunkElems / 8 : (int)(last_elems >> 3);
+          st_final_chunk(buf, ngroups, elem0, tv2, tvf, inv_T, eps, a1, a2, u1, b1, t1);
+        }
+        if (a1 > published) { atomicMax(&ctl.best_key, f32_key(a1)); published = a1; }
+        if (__syncthreads_or(!arrived)) {
+          if (threadIdx.x == 0) *p.error_flag = 1;
+          return;
+        }
+        if (threadIdx.x == 0) st_issue(p, ps, order, ring, ctl, slot);
+        if (++slot == kStSlots) { slot = 0; phase ^= 1u; }
+      }
+      if (res >= 0) {
+        // the item's record: its best element, and whether anything else of it comes within the slack
+        const uint32_t key = f32_key(a1);
+        const uint32_t wkey = __reduce_max_sync(0xFFFFFFFFu, key);
+        const int wtok = __reduce_min_sync(0xFFFFFFFFu, key == wkey ? t1 : 0x7FFFFFFF);
+        if (lane == 0) { ctl.wkey[warp] = wkey; ctl.wtok[warp] = wtok; }
+        __syncthreads();
+        uint32_t bkey = ctl.wkey[0];
+        int btok = ctl.wtok[0];
+#pragma unroll 1
+        for (int i = 1; i < kStWarps; ++i) {
+          const uint32_t k = ctl.wkey[i];
+          const int tk = ctl.wtok[i];
+          if (k > bkey || (k == bkey && tk < btok)) { bkey = k; btok = tk; }
+        }
+        const bool any = btok != 0x7FFFFFFF;
+        const bool mine = any ? (key == bkey && t1 == btok) : threadIdx.x == 0;
+        const float amax = key_f32(bkey);
+        const float cut = amax - (kGumbelSlack + 1e-5f * fabsf(amax));
+        const int multi = __syncthreads_or(any && ((!mine && a1 >= cut) || a2 >= cut));
+        if (mine) {
+          FinRecord r;
+          r.a = a1; r.u = u1; r.tok = any ? t1 : 0x7FFFFFFF; r.bits = b1 | (multi ? 0x10000u : 0u);
+          p.records[(size_t)row * p.nfin + part] = r;
+          if (any) atomicMax(&p.wstate[row].best_key, bkey);
+        }
+      }
+      __syncthreads();   // the producer's fifo entries are visible; ctl is free again
+      if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + 3;
+      continue;
+    }
     const uint32_t dw = dtab[row];
     const int cls = (int)(dw >> 16), key16 = (int)(dw & 0xFFFFu);
     const int c0 = part * p.part_chunks;
@@ -656,7 +858,7 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 10] = global_timer_ns() - tl_t;
 #endif
         const int v = st_wide_threshold(p, row, key16, p.sp.top_p[row], area, ctl.wide);
-        if (threadIdx.x == 0) { p.wstate[row].kmax16 = ctl.wide.kmax16; p.wstate[row].vstar16 = v; }
+        if (threadIdx.x == 0) *reinterpret_cast<volatile int*>(&p.wstate[row].result) = wide_result(ctl.wide.kmax16, v);
 #ifdef TLX_TIMELINE
         if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 11] = global_timer_ns() - tl_t;
 #endif
@@ -758,7 +960,7 @@ __device__ __forceinline__ int st_finish_normal(const StreamParams& p, int row, 
   const int nseg = p.P * kStWarps;
   const int lane = lane_id(), warp = warp_id();
   const int64_t nrow = row + sp.dim0_offset;
-  const float* noise_row = sp.noise.dense ? sp.noise.dense + nrow * sp.noise.stride : nullptr;
+  const float* noise_row = sp.noise.dense ? sp.noise.dense_row(nrow) : nullptr;
   // ---- one round trip: every segment's count and its first kStSpec entries (thread = segment and half)
   constexpr int kSubs = kStSpec / 16;   // threads per segment
   const uint32_t* cbase = p.cands + (size_t)row * nseg * kStWarpCap;
@@ -1058,36 +1260,6 @@ static __device__ __noinline__ void st_slow_row(const StreamParams& p, int row, 
   }
 }
 
-static __device__ __forceinline__ void st_finish_row(const StreamParams& p, int row, unsigned char* smem) {
-  TailShared& t = *reinterpret_cast<TailShared*>(smem);
-  const SampleParams& sp = p.sp;
-  for (int i = threadIdx.x; i < kTlBins; i += kStThreads) t.hist[i] = 0;
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // the stream kernel's lists and thresholds are complete
-  // one round trip for everything the row's short path reads first (whatever the row's class turns out to be)
-  const StreamDesc d = p.desc[row];
-  const float pp = sp.top_p[row], T_ = sp.temperature[row];
-  const int timeout = __ldcg(p.error_flag) ? (int)kStatusTimeout : 0;
-  const TailFetch fetched = tl_fetch(p, row);
-  TLX_STAMP(sp, 0);
-  __syncthreads();
-  bool slow = d.cls == kStOther;
-  if (d.cls == kStNormal) {
-    TLX_STAMP(sp, 1);
-    const int tok = st_finish_normal(p, row, d, pp, T_, fetched, t);
-    slow = tok < 0;   // threshold too high for this row, a list overflowed, or keys too far apart
-    if (!slow && threadIdx.x == 0) {
-      sp.out_tokens[row] = tok;
-      if (sp.out_status) sp.out_status[row] = timeout;
-    }
-  } else if (d.cls == kStWide) {
-    slow = __ldcg(&p.wstate[row].vstar16) < 0;   // the window did not settle the threshold
-    if (!slow && threadIdx.x == 0 && sp.out_status) atomicOr(sp.out_status + row, (int)kStatusGeneral | timeout);
-  }
-  TLX_STAMP(sp, 8);
-  if (threadIdx.x == 0 && sp.timeline) sp.timeline[(size_t)blockIdx.x * 16 + 9] = d.cls;
-  if (slow) st_slow_row(p, row, smem);
-}
-
 // ---- finish: final pass over the wide rows ------------------------------------------------------------
 // One CTA per (wide row, range of the row's 8 KB chunks); the ranges are as short as the number of
 // final-pass CTAs allows, so that the pass is a single wave.  A CTA keeps, per thread, the two best
@@ -1107,14 +1279,16 @@ __device__ __forceinline__ void fin_issue(const StreamParams& p, int row, int c,
   mbar_expect_tx(&mbar[slot], dense ? bytes * 3 : bytes);
   bulk_load(dst, src, bytes, &mbar[slot]);
   if (dense) {
-    const float* nsrc = p.sp.noise.dense + (row + p.sp.dim0_offset) * p.sp.noise.stride + (int64_t)c * kFinChunkElems;
+    const float* nsrc = p.sp.noise.dense_row(row + p.sp.dim0_offset) + (int64_t)c * kFinChunkElems;
     bulk_load(dst + kFinChunk, nsrc, bytes * 2, &mbar[slot]);
   }
 }
 
 // Decides a wide row from the records of its ranges (all threads of the CTA that delivered the last one;
 // at most kStThreads records).
-__device__ __forceinline__ void fin_decide_row(const StreamParams& p, int row, int nrec, StControl& ctl) {
+// range_elems > 0: record i covers the elements [i * range_elems, (i + 1) * range_elems); 0: the final
+// pass's ranges of chunks.
+__device__ __forceinline__ void fin_decide_row(const StreamParams& p, int row, int nrec, int range_elems, StControl& ctl) {
   const SampleParams& sp = p.sp;
   const FinRecord* recs = p.records + (size_t)row * p.nfin;
   const float T_ = sp.temperature[row];
@@ -1145,7 +1319,7 @@ __device__ __forceinline__ void fin_decide_row(const StreamParams& p, int row, i
   __syncthreads();
   if (lane == 0) ctl.wkey[warp] = again;
   __syncthreads();
-  const uint32_t vstar16 = (uint32_t)__ldcg(&p.wstate[row].vstar16);
+  const uint32_t vstar16 = (uint32_t)wide_vstar16(__ldcg(&p.wstate[row].result));
   const float tvf = __uint_as_float(key16_bf16_bits(vstar16) << 16);
   const __nv_bfloat16* rowp = reinterpret_cast<const __nv_bfloat16*>(sp.logits) + (int64_t)row * sp.row_stride;
   for (int w = 0; w < kStWarps; ++w) {
@@ -1153,8 +1327,8 @@ __device__ __forceinline__ void fin_decide_row(const StreamParams& p, int row, i
     while (mask) {
       const int i = w * 32 + __ffs(mask) - 1;
       mask &= mask - 1;
-      const int64_t e0 = (int64_t)((int64_t)i * p.nfin / nrec) * kFinChunkElems;
-      int64_t e1 = (int64_t)((int64_t)(i + 1) * p.nfin / nrec) * kFinChunkElems;
+      const int64_t e0 = range_elems > 0 ? (int64_t)i * range_elems : (int64_t)((int64_t)i * p.nfin / nrec) * kFinChunkElems;
+      int64_t e1 = range_elems > 0 ? e0 + range_elems : (int64_t)((int64_t)(i + 1) * p.nfin / nrec) * kFinChunkElems;
       e1 = e1 < sp.vocab ? e1 : sp.vocab;
       for (int64_t c = e0 + threadIdx.x; c < e1; c += kStThreads) {
         const uint32_t b = *reinterpret_cast<const unsigned short*>(rowp + c);
@@ -1221,7 +1395,8 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
     const int w = unit / J, j = unit - w * J;
     const int row = wlist[w];
     WideState* ws = p.wstate + row;
-    const int vstar = __ldcg(&ws->vstar16);
+    const int wres = __ldcg(&ws->result);
+    const int vstar = wide_vstar16(wres);
     if (vstar < 0) continue;   // the row's own CTA answers it with the whole-row routines
     const int c_begin = (int)((int64_t)j * p.nfin / J), c_end = (int)((int64_t)(j + 1) * p.nfin / J);
     const uint32_t tbits = key16_bf16_bits((uint32_t)vstar);
@@ -1248,7 +1423,7 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
     // score `cb`, an element whose noise u gives -log(-log u) < cb - xtop - margin cannot come within the
     // screening slack of the best, and -log u <= 1 - u ... so the test is one comparison of 1 - u with
     // eps = exp(-(cb - xtop - margin)) (1 - u >= 1 - exp(-eps') for the exact bound eps'; eps is looser).
-    const float xtop = key16_value(__ldcg(&ws->kmax16)) * inv_T;
+    const float xtop = key16_value(wide_kmax16(wres)) * inv_T;
     float published = -INFINITY;
     for (int c = c_begin; c < c_end; ++c) {
       const float cb = key_f32(ctl.best_key);
@@ -1351,11 +1526,48 @@ static __device__ __forceinline__ void st_final_pass(const StreamParams& p, int 
     if (ctl.flag) {
       __threadfence();
       TLX_STAMP(sp, 6);
-      fin_decide_row(p, row, J, ctl);
+      fin_decide_row(p, row, J, 0, ctl);
       TLX_STAMP(sp, 7);
     }
   }
   TLX_STAMP(sp, 5);
+}
+
+static __device__ __forceinline__ void st_finish_row(const StreamParams& p, int row, unsigned char* smem) {
+  TailShared& t = *reinterpret_cast<TailShared*>(smem);
+  const SampleParams& sp = p.sp;
+  for (int i = threadIdx.x; i < kTlBins; i += kStThreads) t.hist[i] = 0;
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // the stream kernel's lists and thresholds are complete
+  // one round trip for everything the row's short path reads first (whatever the row's class turns out to be)
+  const StreamDesc d = p.desc[row];
+  const float pp = sp.top_p[row], T_ = sp.temperature[row];
+  const int timeout = __ldcg(p.error_flag) ? (int)kStatusTimeout : 0;
+  const TailFetch fetched = tl_fetch(p, row);
+  TLX_STAMP(sp, 0);
+  __syncthreads();
+  bool slow = d.cls == kStOther;
+  if (d.cls == kStNormal) {
+    TLX_STAMP(sp, 1);
+    const int tok = st_finish_normal(p, row, d, pp, T_, fetched, t);
+    slow = tok < 0;   // threshold too high for this row, a list overflowed, or keys too far apart
+    if (!slow && threadIdx.x == 0) {
+      sp.out_tokens[row] = tok;
+      if (sp.out_status) sp.out_status[row] = timeout;
+    }
+  } else if (d.cls == kStWide) {
+    // the window did not settle the threshold, or (final items in the stream kernel) something went wrong there
+    slow = __ldcg(&p.wstate[row].result) < 0 || (p.fin_items > 0 && timeout);
+    if (!slow && p.fin_items > 0) {
+      // the stream kernel has left a record per final item of the row: decide
+      StControl& ctl = *reinterpret_cast<StControl*>(smem + kFinSlots * kFinSlotBytes);
+      __syncthreads();
+      fin_decide_row(p, row, p.fin_items, kStFinalElems, ctl);
+    }
+    if (!slow && threadIdx.x == 0 && sp.out_status) atomicOr(sp.out_status + row, (int)kStatusGeneral | timeout);
+  }
+  TLX_STAMP(sp, 8);
+  if (threadIdx.x == 0 && sp.timeline) sp.timeline[(size_t)blockIdx.x * 16 + 9] = d.cls;
+  if (slow) st_slow_row(p, row, smem);
 }
 
 constexpr size_t kStFinishRowSmem =

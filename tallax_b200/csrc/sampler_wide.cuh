@@ -286,7 +286,7 @@ __global__ void __cluster_dims__(kWideCluster, 1, 1) __launch_bounds__(kThreads,
             }
             if (some[b] && noise_vec) {
               const float4* np4 =
-                  reinterpret_cast<const float4*>(p.noise.dense + nrow * p.noise.stride + ((int64_t)(v0 + i) << 3));
+                  reinterpret_cast<const float4*>(p.noise.dense_row(nrow) + ((int64_t)(v0 + i) << 3));
               nz[b][0] = __ldg(np4);
               nz[b][1] = __ldg(np4 + 1);
             }
@@ -327,7 +327,7 @@ __global__ void __cluster_dims__(kWideCluster, 1, 1) __launch_bounds__(kThreads,
           const __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(bf162_bits(v.x), bf162_bits(v.y)),
                                                __hmax2_nan(bf162_bits(v.z), bf162_bits(v.w)));
           if (!__hblt2(m, thr2))
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.noise.dense + nrow * p.noise.stride + ((int64_t)(v0 + i) << 3)));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.noise.dense_row(nrow) + ((int64_t)(v0 + i) << 3)));
         }
       }
       pass_over(0.f, nullptr);

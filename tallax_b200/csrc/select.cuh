@@ -311,12 +311,70 @@ static __device__ __noinline__ int sort_candidates(uint64_t* cand, int m) {
 //   e_i = exp(x_i - x_0), cs = cumsum(e) / sum(e), t = min(#(cs < p), K-1),
 //   keep x_i >= x_t, y_i = x_i / T + gumbel(u_i), token = arg-max y (ties: lower token).
 // The arg-max is screened in f32 and decided on the f64-evaluated Gumbel term for the
-// contenders only.  K <= kMaxItems * blockDim.x.  All threads call; the result is valid
-// in every thread.
+// contenders only.  All threads call; the result is valid in every thread.
+//
+// sample_tail<kMaxItems> keeps a thread's candidates in registers and serves K <= kMaxItems *
+// blockDim.x; above that it hands over to sample_tail_any, which serves any K by reading the
+// candidates again in every pass (the same sums in the same order, so both give the same token).
+template <typename ValueOf, typename TokenOf, typename NoiseOf>
+static __device__ __noinline__ int sample_tail_any(int K, float p, float T, SelectShared& s, ValueOf value_of,
+                                               TokenOf token_of, NoiseOf noise_of) {
+  const int per = (K + blockDim.x - 1) / blockDim.x;
+  const int i0 = threadIdx.x * per;
+  const int i1 = min(i0 + per, K);
+  const int nw = (blockDim.x + 31) >> 5;
+  const float x0 = value_of(0);
+  double acc = 0.0;
+  for (int i = i0; i < i1; ++i) acc += (double)expf(value_of(i) - x0);
+  double Z;
+  const double base = block_scan_incl<double>(acc, s.scan_f64, &Z, ShflUpF64()) - acc;
+  int below = 0;
+  const double pd = (double)p;
+  double run = 0.0;
+  for (int i = i0; i < i1; ++i) {
+    run += (double)expf(value_of(i) - x0);
+    below += ((base + run) / Z < pd) ? 1 : 0;
+  }
+  uint32_t t_total;
+  block_scan_incl<uint32_t>((uint32_t)below, s.scan_u32, &t_total, ShflUpU32());
+  const int t = min((int)t_total, K - 1);
+  const float thr = value_of(t);
+  float amax = -INFINITY;
+  for (int i = i0; i < i1; ++i) {
+    const float x = value_of(i);
+    if (x >= thr) amax = fmaxf(amax, __fdiv_rn(x, T) + gumbel_screen(noise_of(i)));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  __syncthreads();
+  if (lane_id() == 0) s.scan_f64[warp_id()] = (double)amax;
+  __syncthreads();
+  amax = -INFINITY;
+  for (int w = 0; w < nw; ++w) amax = fmaxf(amax, (float)s.scan_f64[w]);
+  __syncthreads();
+  const float cut = amax - (kGumbelSlack + 1e-5f * fabsf(amax));
+  Best best{-INFINITY, 0x7FFFFFFF};
+  for (int i = i0; i < i1; ++i) {
+    const float x = value_of(i);
+    if (x >= thr) {
+      const float u = noise_of(i);
+      if (__fdiv_rn(x, T) + gumbel_screen(u) >= cut) best = best_of(best, Best{__fdiv_rn(x, T) + gumbel_exact(u), token_of(i)});
+    }
+  }
+  best = warp_best(best);
+  if (lane_id() == 0) { s.scan_f64[warp_id()] = (double)best.y; s.scan_u32[warp_id()] = (uint32_t)best.tok; }
+  __syncthreads();
+  Best b{-INFINITY, 0x7FFFFFFF};
+  for (int w = 0; w < nw; ++w) b = best_of(b, Best{(float)s.scan_f64[w], (int)s.scan_u32[w]});
+  __syncthreads();
+  return b.tok;
+}
+
 template <int kMaxItems, typename ValueOf, typename TokenOf, typename NoiseOf>
 static __device__ __noinline__ int sample_tail(int K, float p, float T, SelectShared& s, ValueOf value_of,
                                            TokenOf token_of, NoiseOf noise_of) {
   const int per = (K + blockDim.x - 1) / blockDim.x;
+  if (per > kMaxItems) return sample_tail_any(K, p, T, s, value_of, token_of, noise_of);
   const int i0 = threadIdx.x * per;
   const float x0 = value_of(0);
   float x[kMaxItems];

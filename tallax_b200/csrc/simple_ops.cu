@@ -197,9 +197,10 @@ static int launch_argmax(cudaStream_t st, const void* keys, int64_t rows, int64_
 // ---------------------------------------------------------------------------------
 // counter-based uniform noise at arbitrary (i0, i1)
 // ---------------------------------------------------------------------------------
-__global__ void sparse_uniform_kernel(uint32_t k0, uint32_t k1, const int32_t* __restrict__ i0,
-                                      const int32_t* __restrict__ i1, int64_t count, int64_t dim1, float minval,
-                                      float maxval, float* __restrict__ out) {
+__global__ void sparse_uniform_kernel(uint32_t k0, uint32_t k1, const uint32_t* __restrict__ key_dev,
+                                      const int32_t* __restrict__ i0, const int32_t* __restrict__ i1, int64_t count,
+                                      int64_t dim1, float minval, float maxval, float* __restrict__ out) {
+  if (key_dev) { k0 = __ldg(key_dev); k1 = __ldg(key_dev + 1); }   // the key as a device operand
   for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < count;
        e += (int64_t)gridDim.x * blockDim.x) {
     const uint32_t ctr = (uint32_t)((int64_t)i0[e] * dim1 + (int64_t)i1[e]);
@@ -282,17 +283,29 @@ int tlx_argmax(void* stream, const void* keys, int dtype, int64_t rows, int64_t 
   }
 }
 
-int tlx_sparse_random_uniform(void* stream, uint32_t key0, uint32_t key1, const int32_t* idx0, const int32_t* idx1,
-                              int64_t count, int64_t dim1_size, float minval, float maxval, float* out) {
+static int sparse_random_uniform_impl(void* stream, uint32_t key0, uint32_t key1, const uint32_t* key_dev,
+                                      const int32_t* idx0, const int32_t* idx1, int64_t count, int64_t dim1_size,
+                                      float minval, float maxval, float* out) {
   cudaStream_t st = (cudaStream_t)stream;
   TLX_CHECK_ARG(count >= 0 && dim1_size > 0, "sparse_random_uniform: bad extent");
   if (count == 0) return TLX_OK;
   TLX_CHECK_ARG(idx0 && idx1 && out, "sparse_random_uniform: null pointer");
   const int64_t want = (count + 255) / 256;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-  sparse_uniform_kernel<<<blocks, 256, 0, st>>>(key0, key1, idx0, idx1, count, dim1_size, minval, maxval, out);
+  sparse_uniform_kernel<<<blocks, 256, 0, st>>>(key0, key1, key_dev, idx0, idx1, count, dim1_size, minval, maxval, out);
   TLX_CHECK_LAUNCH("sparse_random_uniform");
   return TLX_OK;
+}
+
+int tlx_sparse_random_uniform(void* stream, uint32_t key0, uint32_t key1, const int32_t* idx0, const int32_t* idx1,
+                              int64_t count, int64_t dim1_size, float minval, float maxval, float* out) {
+  return sparse_random_uniform_impl(stream, key0, key1, nullptr, idx0, idx1, count, dim1_size, minval, maxval, out);
+}
+
+int tlx_sparse_random_uniform_dev(void* stream, const uint32_t* key_dev, const int32_t* idx0, const int32_t* idx1,
+                                  int64_t count, int64_t dim1_size, float minval, float maxval, float* out) {
+  if (!key_dev) return set_error(TLX_ERR_INVALID, "sparse_random_uniform: null key");
+  return sparse_random_uniform_impl(stream, 0u, 0u, key_dev, idx0, idx1, count, dim1_size, minval, maxval, out);
 }
 
 }  // extern "C"

@@ -224,14 +224,26 @@ __device__ __forceinline__ float gumbel_screen(float u) {
 constexpr float kGumbelSlack = 1e-3f;
 
 // Noise source shared by the samplers: dense tensor or threefry key.
+// The key and the row offset may also be given as device operands (the *_dev entry points): the key as
+// two words in device memory, the offset as an int32 scalar in device memory that is added to every row
+// index.  A caller under a tracing compiler has both only as device buffers.
 struct NoiseSrc {
   const float* dense;     // nullable
   int64_t stride;         // elements per row of `dense`
-  uint32_t k0, k1;        // threefry key
+  uint32_t k0, k1;        // threefry key (unless key_dev)
   int64_t vocab;          // counter = row * vocab + token
+  const uint32_t* key_dev;         // nullable: the key's two words in device memory
+  const int32_t* row_offset_dev;   // nullable: added to the row index
+  __device__ __forceinline__ int64_t row_of(int64_t row) const {
+    return row_offset_dev ? row + (int64_t)__ldg(row_offset_dev) : row;
+  }
+  // start of the noise of a row (dense noise only)
+  __device__ __forceinline__ const float* dense_row(int64_t row) const { return dense + row_of(row) * stride; }
   __device__ __forceinline__ float at(int64_t row, int64_t tok) const {
+    row = row_of(row);
     if (dense) return __ldg(dense + row * stride + tok);
-    float f = threefry_uniform01_call(k0, k1, (uint32_t)(row * vocab + tok));
+    const uint32_t a = key_dev ? __ldg(key_dev) : k0, b = key_dev ? __ldg(key_dev + 1) : k1;
+    float f = threefry_uniform01_call(a, b, (uint32_t)(row * vocab + tok));
     return fmaxf(f, kF32Tiny);
   }
 };

@@ -154,10 +154,11 @@ int tlx_top_k(void* stream, const void* x, int dtype, int64_t rows, int64_t n, i
 
 size_t tlx_shard_candidates_workspace_bytes(int64_t, int64_t, int) { return 0; }
 
-int tlx_shard_candidates(void* stream, const void* logits, int dtype, int64_t rows, int64_t v_local,
-                         int64_t row_stride, int64_t col_offset, int k_cand, const float* noise, int64_t noise_stride,
-                         uint32_t key0, uint32_t key1, int64_t vocab_total, int64_t dim0_offset, float* out_vals,
-                         int32_t* out_idx, float* out_noise, void*, size_t) {
+static int shard_candidates_impl(void* stream, const void* logits, int dtype, int64_t rows, int64_t v_local,
+                                 int64_t row_stride, int64_t col_offset, int k_cand, const float* noise,
+                                 int64_t noise_stride, uint32_t key0, uint32_t key1, const uint32_t* key_dev,
+                                 int64_t vocab_total, int64_t dim0_offset, const int32_t* dim0_offset_dev,
+                                 float* out_vals, int32_t* out_idx, float* out_noise) {
   cudaStream_t st = (cudaStream_t)stream;
   TLX_CHECK_ARG(rows >= 0 && v_local > 0, "shard_candidates: bad extent");
   TLX_CHECK_ARG(k_cand >= 1 && k_cand <= 1024, "shard_candidates: k_cand must be in [1, 1024], got %d", k_cand);
@@ -172,7 +173,26 @@ int tlx_shard_candidates(void* stream, const void* logits, int dtype, int64_t ro
   p.cand_vals = out_vals; p.cand_idx = out_idx; p.cand_noise = out_noise; p.col_offset = col_offset;
   p.dim0_offset = dim0_offset;
   p.noise.dense = noise; p.noise.stride = noise_stride; p.noise.k0 = key0; p.noise.k1 = key1; p.noise.vocab = vocab_total;
+  p.noise.key_dev = key_dev; p.noise.row_offset_dev = dim0_offset_dev;
   return dispatch_topk(st, dtype, p, "shard_candidates");
+}
+
+int tlx_shard_candidates(void* stream, const void* logits, int dtype, int64_t rows, int64_t v_local,
+                         int64_t row_stride, int64_t col_offset, int k_cand, const float* noise, int64_t noise_stride,
+                         uint32_t key0, uint32_t key1, int64_t vocab_total, int64_t dim0_offset, float* out_vals,
+                         int32_t* out_idx, float* out_noise, void*, size_t) {
+  return shard_candidates_impl(stream, logits, dtype, rows, v_local, row_stride, col_offset, k_cand, noise, noise_stride,
+                               key0, key1, nullptr, vocab_total, dim0_offset, nullptr, out_vals, out_idx, out_noise);
+}
+
+int tlx_shard_candidates_dev(void* stream, const void* logits, int dtype, int64_t rows, int64_t v_local,
+                             int64_t row_stride, int64_t col_offset, int k_cand, const float* noise,
+                             int64_t noise_stride, const uint32_t* key_dev, int64_t vocab_total,
+                             const int32_t* dim0_offset_dev, float* out_vals, int32_t* out_idx, float* out_noise,
+                             void*, size_t) {
+  if (!noise && !key_dev) return set_error(TLX_ERR_INVALID, "shard_candidates: neither noise nor a key given");
+  return shard_candidates_impl(stream, logits, dtype, rows, v_local, row_stride, col_offset, k_cand, noise, noise_stride,
+                               0u, 0u, key_dev, vocab_total, 0, dim0_offset_dev, out_vals, out_idx, out_noise);
 }
 
 }  // extern "C"

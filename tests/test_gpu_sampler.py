@@ -216,3 +216,56 @@ def test_vocab_sharded_entry_point_single_rank(cuda):
     got = sampling.sample_vocab_sharded(None, to_dev(x, cuda), md, noise_shard=to_dev(noise, cuda), k_cand=50)
     exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
     _assert_tokens(to_np(got), exp, flags, min_checked=0.7)
+
+
+@pytest.mark.parametrize("seed", [31, 32, 33])
+def test_sample_f32_top_k_between_1025_and_2048(cuda, seed):
+    # more rows than SMs, every row with a top_k that the candidate path serves but that exceeds
+    # 2 x (threads per CTA) candidates in the tail
+    B, V = 160, 40000
+    x, tk, tp, T, noise = o.make_sampling_inputs(B=B, V=V, seed=seed, dtype="f32")
+    tk[:] = np.random.default_rng(seed).integers(1025, 2049, B).astype(np.int32)
+    tk[:4] = [1025, 2048, 2047, 1536]
+    tp[::3] = 1.0   # the whole top-k set is kept: the tail walks all of its candidates
+    exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
+    got, status = _run(cuda, x, tk, tp, T, noise=noise)
+    _assert_tokens(got, exp, flags, min_checked=0.6)   # top_p == 1 sits on the threshold by construction
+    assert (status & 2 == 0).all()
+
+
+def test_sample_bf16_top_k_2000_over_few_finite_logits(cuda):
+    B, V = 12, 50000
+    x, tk, tp, T, noise = o.make_sampling_inputs(B=B, V=V, seed=41, dtype="bf16")
+    rng = np.random.default_rng(41)
+    xf = x.astype(np.float32)
+    for b in range(B):
+        keep = rng.choice(V, size=100, replace=False)
+        m = np.full(V, -np.inf, np.float32)
+        m[keep] = xf[b, keep]
+        xf[b] = m
+    x = xf.astype(x.dtype)
+    tk[:] = 2000
+    tp[:] = np.linspace(0.5, 1.0, B).astype(np.float32)
+    exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
+    got, _ = _run(cuda, x, tk, tp, T, noise=noise)
+    _assert_tokens(got, exp, flags, min_checked=0.7)
+    assert np.isfinite(x.astype(np.float32)[np.arange(B), got]).all()
+
+
+@pytest.mark.parametrize("top_k", [0, 1500, 2048])
+def test_merge_and_sample_with_more_than_1024_candidates(cuda, top_k):
+    # 8 shards x 256 candidates: with top-k disabled (or large) the tail walks all 2048 of them
+    B, V, n_shards, k_cand = 16, 65536, 8, 256
+    x, _, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=6, dtype="bf16")
+    tk = np.full(B, top_k, np.int32)
+    tp[::4] = 0.9999   # nearly the whole candidate set is kept: the tail walks all of it
+    vl = V // n_shards
+    parts = [o.shard_candidates(x[:, s * vl:(s + 1) * vl], s * vl, k_cand, noise[:, s * vl:(s + 1) * vl])
+             for s in range(n_shards)]
+    cv, ci, cn = (np.concatenate([p[i] for p in parts], axis=1) for i in range(3))
+    exp, flags = o.merge_and_sample(cv, ci, cn, tk, tp, T, return_flags=True)
+    dx, dn = to_dev(x, cuda), to_dev(noise, cuda)
+    blocks = [ops.shard_candidates(dx[:, s * vl:(s + 1) * vl].contiguous(), s * vl, k_cand,
+                                   noise_shard=dn[:, s * vl:(s + 1) * vl].contiguous()) for s in range(n_shards)]
+    got = ops.merge_and_sample(torch.stack(blocks), to_dev(tk, cuda), to_dev(tp, cuda), to_dev(T, cuda))
+    _assert_tokens(to_np(got), exp, flags, min_checked=0.7)
