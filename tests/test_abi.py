@@ -71,3 +71,27 @@ def test_python_mirror_error_behaviour():
         top_p_mask(topk_logits=torch.zeros(4, 4), p=torch.zeros(4), replace_val=0.0, axis=1)
     with pytest.raises(ValueError):
         tax.cumsum(torch.zeros(4, 4), axis=0)  # CPU tensor: there is no CPU path
+
+
+def test_xla_ffi_adapter_compiles_without_xla_and_binds_declared_symbols(tmp_path):
+    import shutil
+    import subprocess
+    src = os.path.join(ROOT, "tallax_b200", "ffi", "xla_ffi_adapter.cc")
+    text = open(src).read()
+    used = set(re.findall(r"\b(tlx_[a-z0-9_]+)\s*\(", re.sub(r"//.*", "", text)))
+    assert {"tlx_sample_dev", "tlx_top_p_and_sample_dev", "tlx_gumbel_argmax_dev", "tlx_sparse_random_uniform_dev",
+            "tlx_shard_candidates_dev"} <= used
+    assert used <= set(_declared()), used - set(_declared())
+    gxx = shutil.which("g++")
+    if gxx:   # no XLA headers here: the guard leaves an empty object
+        obj = str(tmp_path / "ffi.o")
+        subprocess.run([gxx, "-std=c++17", "-fPIC", "-I", os.path.join(ROOT, "include"), "-c", src, "-o", obj], check=True)
+
+
+def test_device_operand_entry_points_reject_missing_key_without_gpu():
+    lib = _lib.load()
+    rc = lib.tlx_sample_dev(None, None, _lib.TLX_BF16, 4, 128256, 128256, None, None, None, None, 0, None, None, None,
+                            None, None, 0)
+    assert rc == _lib.TLX_ERR_INVALID and b"key" in lib.tlx_last_error()
+    rc = lib.tlx_gumbel_argmax_dev(None, None, None, None, 4, 4, None, 16, 1, None)
+    assert rc == _lib.TLX_ERR_INVALID
