@@ -6,7 +6,14 @@
 One "step" is one fused-sampler call over one batch (256 rows per GPU, weak scaling:
 batch rows are independent, each rank samples its own batch, no collective on the data
 path).  Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of
-the reference's algorithm on the host cores instead (rank 0 only).
+the reference's algorithm on the host cores instead (rank 0 only), on the 256 rows of the
+same input set 0 that the GPU arm's first step reads.
+
+Side records in the same line: `replay_200` (200 further graph launches, a steadier mean),
+`e2e_key_noise` (end to end with threefry noise from a key instead of an uploaded noise
+tensor), and with more than one GPU `strong` (the 256 rows split over the ranks,
+dim0_offset = rank * 256 / N) and `vocab_sharded` (benchmark configuration 5: the vocabulary
+split over the ranks, NCCL all-gather of the candidates).
 """
 from __future__ import annotations
 
@@ -26,7 +33,7 @@ if ROOT not in sys.path:
 B, V = 256, 128256          # benchmark configuration: decode batch and vocabulary (Llama-3 sized)
 N_SETS = 4                  # rotating input sets: 4 x 65.7 MB of logits > 126 MB L2, so every step reads HBM
 ALGO_BYTES = B * V * 2 + B * 12 + B * 4   # logits once + three parameter vectors + tokens out
-NCU_TRAFFIC_BYTES = 80085760   # dram__bytes_read.sum + dram__bytes_write.sum over one call's two kernels (profiles/)
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "ncu_dram_traffic_sample_c3.json")   # from one ncu capture
 METRIC, UNIT = "sampled_tokens_per_s", "tokens/s"
 WORKLOAD = ("fused temperature/top-k/top-p/noise sampling, bf16 logits [256,128256] = N(0,sigma=3) + 10 at 8 "
             "columns per row, T~U[0.5,1.5], top_k~U{1..1024} with 10% disabled, top_p~U[0.6,1), explicit f32 "
@@ -89,20 +96,39 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def make_inputs(torch, device, seed):
-    """One synthetic input set with the configuration's shapes and distributions, made on the device."""
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    x = torch.randn((B, V), generator=g, device=device, dtype=torch.float32) * 3.0
-    cols = torch.rand((B, V), generator=g, device=device).argsort(dim=1)[:, :8]
-    x.scatter_add_(1, cols, torch.full((B, 8), 10.0, device=device))
-    logits = x.to(torch.bfloat16)
-    temperature = torch.rand(B, generator=g, device=device) + 0.5
-    top_k = torch.randint(1, 1025, (B,), generator=g, device=device, dtype=torch.int32)
-    top_k[torch.rand(B, generator=g, device=device) < 0.1] = 0
-    top_p = torch.rand(B, generator=g, device=device) * 0.4 + 0.6
-    noise = torch.rand((B, V), generator=g, device=device, dtype=torch.float32)
-    return logits, top_k, top_p, temperature, noise
+def ncu_traffic():
+    """dram bytes read + written by the kernels of one sampler call, from the committed summary of an ncu
+    capture of this workload (None if the file is missing)."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            return int(json.load(f)["dram_bytes_per_call"])
+    except Exception:
+        return None
+
+
+def make_inputs_host(seed, rows=B):
+    """One synthetic input set with the configuration's shapes and distributions, as NumPy arrays (Philox
+    stream `seed`).  Both arms draw their inputs here, so that they sample the same rows."""
+    import ml_dtypes
+    import numpy as np
+    rng = np.random.Generator(np.random.Philox(seed))
+    x = rng.standard_normal((rows, V), dtype=np.float32) * np.float32(3.0)
+    cols = np.argsort(rng.random((rows, 64), dtype=np.float32), axis=1)[:, :8] * (V // 64) + rng.integers(0, V // 64, (rows, 8))
+    np.add.at(x, (np.arange(rows)[:, None], cols), np.float32(10.0))
+    temperature = rng.uniform(0.5, 1.5, size=rows).astype(np.float32)
+    top_k = rng.integers(1, 1025, size=rows).astype(np.int32)
+    top_k[rng.random(rows) < 0.1] = 0
+    top_p = rng.uniform(0.6, 1.0, size=rows).astype(np.float32)
+    noise = rng.random((rows, V), dtype=np.float32)
+    return x.astype(ml_dtypes.bfloat16), top_k, top_p, temperature, noise
+
+
+def make_inputs(torch, device, seed, rows=B):
+    """The same input set on the device."""
+    x, top_k, top_p, temperature, noise = make_inputs_host(seed, rows)
+    logits = torch.from_numpy(x.view("int16")).view(torch.bfloat16).to(device)
+    return (logits, torch.from_numpy(top_k).to(device), torch.from_numpy(top_p).to(device),
+            torch.from_numpy(temperature).to(device), torch.from_numpy(noise).to(device))
 
 
 def to_numpy(t):
@@ -131,9 +157,11 @@ def run_reference(args):
     import multiprocessing as mp
     from oracle import tallax_oracle as o
     cores = os.cpu_count() or 1
-    rows = 64  # bounded sample of the 256-row batch per step
+    # all 256 rows of input set 0 (the set the GPU arm's first step reads); with few host cores a bounded
+    # sample of its first rows, so that the run still ends within minutes
+    rows = B if cores >= 16 else max(cores, 8) * 4
     workers = min(cores, rows)
-    _REF_DATA = (*o.make_sampling_inputs(B=rows, V=V, seed=2, dtype="bf16"), workers)
+    _REF_DATA = (*(a[:rows] for a in make_inputs_host(0)), workers)
     chunks = list(range(workers))
     with mp.get_context("fork").Pool(workers) as pool:  # forked after the data exists: workers inherit it
         for _ in range(args.warmup):
@@ -147,9 +175,10 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch_per_step": rows},
+        "config": {"workload": WORKLOAD, "batch_per_step": rows, "vocab": V},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": len(chunks), "kind": "port",
-                         "sample": f"{rows} of the 256 rows per step, NumPy restatement (JAX is not installable here)"},
+                         "sample": f"{'all' if rows == B else 'the first'} {rows} of the 256 rows of input set 0 per "
+                                   "step, NumPy restatement (JAX is not installable here)"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -173,8 +202,9 @@ def run_ours(args):
     from tallax_b200._src import ops
     _lib.load()
 
-    sets = [make_inputs(torch, device, seed=1000 * rank + s) for s in range(N_SETS)]
-    ws = ops.SampleWorkspace(B, V, device)
+    rows_call = args.rows_per_call or B   # 32 / 64 / 128: the same rows in smaller calls (a smaller decode batch)
+    sets = [make_inputs(torch, device, seed=1000 * rank + s, rows=rows_call) for s in range(N_SETS)]
+    ws = ops.SampleWorkspace(rows_call, V, device)
     meta = [sampling.SamplingMetadata(top_k=s[1], top_p=s[2], temperature=s[3]) for s in sets]
 
     def step(i):
@@ -225,56 +255,118 @@ def run_ours(args):
         time.sleep(0.1)
     ms = start.elapsed_time(stop)
     rank_ms = ms
+    # a steadier mean: 200 further graph launches
+    replay_ms = None
+    if graphs:
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        r0.record()
+        for i in range(200):
+            graphs[i % N_SETS].replay()
+        r1.record()
+        barrier()
+        replay_ms = r0.elapsed_time(r1) / 200
 
     # ---- end to end through the public API from pinned host buffers --------------------------
-    h_logits = torch.empty((B, V), dtype=torch.bfloat16).pin_memory()
-    h_noise = torch.empty((B, V), dtype=torch.float32).pin_memory()
-    h_params = [torch.empty(B, dtype=t.dtype).pin_memory() for t in sets[0][1:4]]
+    h_logits = torch.empty((rows_call, V), dtype=torch.bfloat16).pin_memory()
+    h_noise = torch.empty((rows_call, V), dtype=torch.float32).pin_memory()
+    h_params = [torch.empty(rows_call, dtype=t.dtype).pin_memory() for t in sets[0][1:4]]
     h_logits.copy_(sets[0][0]); h_noise.copy_(sets[0][4])
     for h, t in zip(h_params, sets[0][1:4]):
         h.copy_(t)
     d_logits, d_noise = torch.empty_like(sets[0][0]), torch.empty_like(sets[0][4])
     d_params = [torch.empty_like(t) for t in sets[0][1:4]]
-    h_tokens = torch.empty(B, dtype=torch.int32).pin_memory()
+    h_tokens = torch.empty(rows_call, dtype=torch.int32).pin_memory()
+    key = (0x243F6A88, 0x85A308D3)
 
-    def e2e_step():
+    def e2e_step(with_noise=True):
         d_logits.copy_(h_logits, non_blocking=True)
-        d_noise.copy_(h_noise, non_blocking=True)
+        if with_noise:
+            d_noise.copy_(h_noise, non_blocking=True)
         for d, h in zip(d_params, h_params):
             d.copy_(h, non_blocking=True)
         md = sampling.SamplingMetadata(top_k=d_params[0], top_p=d_params[1], temperature=d_params[2])
-        tok = sampling.sample(None, d_logits, md, noise=d_noise, workspace=ws)
+        if with_noise:
+            tok = sampling.sample(None, d_logits, md, noise=d_noise, workspace=ws)
+        else:   # the reference's own calling convention: a PRNG key, the noise is generated where it is needed
+            tok = sampling.sample(key, d_logits, md, workspace=ws)
         h_tokens.copy_(tok, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller needs the token ids before the next decode step
 
     e2e_steps = max(3, min(args.steps, 20))
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
 
-    times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+    def time_e2e(with_noise):
+        for _ in range(2):
+            e2e_step(with_noise)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step(with_noise)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    e2e_ms = time_e2e(True)
+    e2e_key_ms = time_e2e(False)
+
+    # ---- the 256 rows split over the ranks (strong scaling): rank r samples rows [r*B/N, (r+1)*B/N) of ONE
+    # global batch, its noise counters offset by dim0_offset = r*B/N, as the reference's batch sharding does
+    strong_ms = None
+    if world > 1 and B % world == 0 and not args.rows_per_call:
+        bl = B // world
+        g_sets = [make_inputs(torch, device, seed=5000 + s) for s in range(N_SETS)]   # the same on every rank
+        s_sets = [tuple(t[rank * bl:(rank + 1) * bl].contiguous() for t in gs[:4]) for gs in g_sets]
+        del g_sets
+        s_ws = ops.SampleWorkspace(bl, V, device)
+        s_meta = [sampling.SamplingMetadata(top_k=t[1], top_p=t[2], temperature=t[3]) for t in s_sets]
+
+        def strong_step(i):
+            return sampling.sample(key, s_sets[i % N_SETS][0], s_meta[i % N_SETS], workspace=s_ws,
+                                   dim0_offset=rank * bl)
+
+        for i in range(4):
+            strong_step(i)
+        barrier()
+        s_graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for j in range(N_SETS):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    strong_step(j)
+                s_graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        for g in s_graphs:
+            g.replay()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for i in range(100):
+            s_graphs[i % N_SETS].replay()
+        s1.record()
+        barrier()
+        strong_ms = s0.elapsed_time(s1) / 100
+
+    # ---- benchmark configuration 5 on the same ranks: the vocabulary split, one all-gather of candidates
+    vs = vocab_sharded_record(args, torch, dist, device, rank, world) if world > 1 and not args.rows_per_call else None
+
+    times = torch.tensor([ms, e2e_ms, e2e_key_ms, strong_ms or 0.0, replay_ms or 0.0], dtype=torch.float64, device=device)
     per_rank = [rank_ms]
     if world > 1:
         gathered = [torch.zeros(1, dtype=torch.float64, device=device) for _ in range(world)]
         dist.all_gather(gathered, times[:1].clone())
         per_rank = [float(t.item()) for t in gathered]
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = times.tolist()
+    ms, e2e_ms, e2e_key_ms, strong_ms, replay_ms = times.tolist()
 
     if rank == 0:
         peak, peak_src = peaks()
         per_step_s = ms / 1e3 / args.steps
-        achieved = ALGO_BYTES / per_step_s / 1e9
         # CPU baseline on a bounded sample of the same workload (rank 0, one core), also a parity spot check
         from oracle import tallax_oracle as o
-        n_cpu = 48
+        n_cpu = min(48, rows_call)
         s0 = sets[0]
         xs, tk, tp, T = (to_numpy(t[:n_cpu]) for t in s0[:4])
         nz = to_numpy(s0[4][:n_cpu])
@@ -283,30 +375,52 @@ def run_ours(args):
         cpu_dt = time.perf_counter() - t0
         got = to_numpy(sampling.sample(None, s0[0], meta[0], noise=s0[4])[:n_cpu])
         mismatches = int(((got != exp) & ~flags).sum())
+        launches_call = launches // max(args.steps, 1)
+        algo = ALGO_BYTES * rows_call // B
+        achieved = algo / per_step_s / 1e9
+        traffic = ncu_traffic() if rows_call == B else None
         line = {
-            "metric": METRIC, "value": world * B * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
+            "metric": METRIC, "value": world * rows_call * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_gpu": B, "vocab": V, "sharding": f"batch rows x{world}",
-                       "l2": f"{N_SETS} rotating input sets ({N_SETS * B * V * 2 / 1e6:.0f} MB of logits > 126 MB L2)"},
+            "config": {"workload": WORKLOAD, "batch_per_gpu": rows_call, "vocab": V, "sharding": f"batch rows x{world}",
+                       "l2": f"{N_SETS} rotating input sets ({N_SETS * rows_call * V * 6 / 1e6:.0f} MB of logits and "
+                             "noise > 126 MB L2)"},
             "clocks": clocks.summary(),
             "ms_per_step_by_rank": [t / args.steps for t in per_rank],
             "launch": "one CUDA graph launch per step" if graphs else "one library call per step",
-            "e2e": {"value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
-                    "h2d_bytes_per_step": B * V * 2 + B * V * 4 + B * 12, "d2h_bytes_per_step": B * 4,
-                    "ms_per_step": e2e_ms / e2e_steps},
+            "e2e": {"value": world * rows_call * e2e_steps / (e2e_ms / 1e3), "unit": UNIT,
+                    "h2d_bytes_per_step": rows_call * V * 2 + rows_call * V * 4 + rows_call * 12,
+                    "d2h_bytes_per_step": rows_call * 4, "ms_per_step": e2e_ms / e2e_steps},
+            "e2e_key_noise": {"value": world * rows_call * e2e_steps / (e2e_key_ms / 1e3), "unit": UNIT,
+                              "h2d_bytes_per_step": rows_call * V * 2 + rows_call * 12, "d2h_bytes_per_step": rows_call * 4,
+                              "ms_per_step": e2e_key_ms / e2e_steps,
+                              "note": "the reference's calling convention: a PRNG key instead of an uploaded noise "
+                                      "tensor (threefry noise generated on the device)"},
             "gpu_launches": int(launches),
+            "replay_200": None if not replay_ms else {"ms_per_step": replay_ms,
+                                                      "value": world * rows_call / (replay_ms / 1e3), "unit": UNIT},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES, "peak_source": peak_src,
-                         "note": "algorithmic bytes of one sampler call / mean duration of the whole call (all of its "
-                                 f"{launches // max(args.steps, 1)} kernels, which together read the logits once), "
-                                 "CUDA events on the launching stream; traffic = dram read+write of the call's "
-                                 "kernels from one ncu capture of this workload"},
+                         "traffic": traffic, "peak_source": peak_src,
+                         "note": "algorithmic bytes of one sampler call (logits once, parameters, tokens) / mean "
+                                 f"duration of the whole call (its {launches_call} kernels: prologue, stream, finish), "
+                                 "CUDA events on the launching stream; the stream kernel is the dominant one and the "
+                                 "only one that reads the logits in full; traffic = dram read+write of the call's "
+                                 "kernels, from profiles/ncu_dram_traffic_sample_c3.json (one ncu capture of this "
+                                 "workload; it includes the noise of the rows without top-k, which the algorithmic "
+                                 "bytes leave out)"},
             "cpu_baseline": {"value": n_cpu / cpu_dt, "unit": UNIT, "cores": 1, "kind": "port",
                              "sample": f"first {n_cpu} rows of input set 0, NumPy restatement of the reference "
                                        f"(JAX not installable here); {mismatches} token mismatches vs the GPU "
                                        f"outside the 1e-6 top-p exemption"},
         }
+        if strong_ms:
+            line["strong"] = {"rows_per_gpu": B // world, "ms_per_step": strong_ms, "value": B / (strong_ms / 1e3),
+                              "unit": UNIT, "scaling": "strong", "steps": 100,
+                              "note": "one global batch of 256 rows split over the ranks, dim0_offset = rank * rows_per_gpu, "
+                                      "threefry noise from one key; max over ranks"}
+        if vs:
+            line["vocab_sharded"] = vs
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -377,18 +491,10 @@ def run_op_workload(args):
                      "traffic": None, "peak_source": peak_src, "note": note}}), flush=True)
 
 
-def run_vocab_sharded(args):
+def vocab_sharded_record(args, torch, dist, device, rank, world, steps=30):
     """Configuration 5: bf16 [1024, 151936] sharded along the vocabulary over the ranks (strong scaling).
-    One step = local top-k' per shard, NCCL all-gather of the candidates, merge and sample."""
-    import torch
-    import torch.distributed as dist
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    One step = local top-k' per shard, NCCL all-gather of the candidates, merge and sample.  Returns the
+    record on rank 0, None elsewhere.  The process group (if world > 1) is the caller's."""
     from tallax_b200 import _lib, sampling
     lib = _lib.load()
     rows, vocab, k = 1024, 151936, 50
@@ -406,10 +512,11 @@ def run_vocab_sharded(args):
     md = sampling.SamplingMetadata(top_k=torch.full((rows,), k, dtype=torch.int32, device=device),
                                    top_p=torch.full((rows,), 0.95, device=device),
                                    temperature=torch.full((rows,), 0.8, device=device))
+    vws = sampling.VocabShardedWorkspace(rows, k, world, device)
     mismatches = None
     if rank == 0:
-        whole = sampling.sample(None, x, md, noise=noise)
-    tok = sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k)
+        whole = sampling.sample(None, x[:, :vl * world], md, noise=noise[:, :vl * world]).clone()
+    tok = sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws)
     if rank == 0:
         mismatches = int((whole != tok).sum())
     del x, noise
@@ -421,17 +528,17 @@ def run_vocab_sharded(args):
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k)
+        sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws)
     barrier()
     total = 0.0
     launches0 = lib.tlx_kernel_launches()
-    with ClockSampler(local_rank) as clocks:
-        for i in range(args.steps):
+    with ClockSampler(device.index) as clocks:
+        for i in range(steps):
             flush.fill_(i & 0xFF)
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k)
+            sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws)
             e1.record()
             e1.synchronize()
             total += e0.elapsed_time(e1)
@@ -439,24 +546,41 @@ def run_vocab_sharded(args):
     t = torch.tensor([total], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
-    if rank == 0:
-        peak, peak_src = peaks()
-        algo = rows * vl * 2 + rows * k * 12        # this rank's logits once + its candidates out
-        achieved = algo / (ms / 1e3) / 1e9
-        print(json.dumps({
-            "metric": METRIC, "value": rows / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "c5: bf16 [1024,151936] = N(0,2) + 4*rank^-1.1, T=0.8, top_k=50, top_p=0.95, "
-                                   "vocab split over the ranks, k'=50 candidates per shard, NCCL all-gather",
-                       "l2": "256 MB flush buffer written between steps"},
-            "clocks": clocks.summary(), "gpu_launches": int(launches),
-            "parity": f"{mismatches} of {rows} tokens differ from the unsharded fused sampler on rank 0",
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
-                         "note": "per GPU: its logits slice once + candidates, over the whole step "
-                                 "(shard kernel, all-gather, merge kernel)"}}), flush=True)
+    ms = float(t.item()) / steps
+    if rank != 0:
+        return None
+    peak, peak_src = peaks()
+    algo = rows * vl * 2 + rows * k * 12        # this rank's logits once + its candidates out
+    achieved = algo / (ms / 1e3) / 1e9
+    return {
+        "metric": METRIC, "value": rows / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "c5: bf16 [1024,151936] = N(0,2) + 4*rank^-1.1, T=0.8, top_k=50, top_p=0.95, "
+                               "vocab split over the ranks, k'=50 candidates per shard, NCCL all-gather",
+                   "l2": "256 MB flush buffer written between steps"},
+        "clocks": clocks.summary(), "gpu_launches": int(launches),
+        "mismatches": mismatches,
+        "parity": f"{mismatches} of {rows} tokens differ from the unsharded fused sampler on rank 0",
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src,
+                     "note": "per GPU: its logits slice once + candidates, over the whole step "
+                             "(shard kernel, all-gather, merge kernel)"}}
+
+
+def run_vocab_sharded(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    rec = vocab_sharded_record(args, torch, dist, device, rank, world, steps=args.steps)
+    if rec is not None:
+        print(json.dumps(rec), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -464,10 +588,12 @@ def run_vocab_sharded(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="time plain library calls instead of CUDA graph launches")
+    ap.add_argument("--rows-per-call", type=int, default=0, choices=[0, 32, 64, 128],
+                    help="time calls of this many rows instead of 256 (the small-batch paths)")
     ap.add_argument("--workload", default="c3", help="c3 (default, the fused sampler) | c1 | c2 | c4a | "
                     "c4a-single-pass | c4b: the other operators at their benchmark sizes, one GPU, rows/s | c5: the "
                     "vocab-sharded sampler over the ranks of torchrun")

@@ -330,13 +330,14 @@ def shard_candidates(logits_shard, col_offset: int, k_cand: int, *, noise_shard=
     return out
 
 
-def merge_and_sample(gathered, top_k_, top_p, temperature):
+def merge_and_sample(gathered, top_k_, top_p, temperature, out=None):
     """gathered: [n_shards, 3, rows, k'] float32 storage as produced by all-gathering `shard_candidates` blocks."""
     gathered = _dev(gathered)
     n_shards, three, rows, k = gathered.shape
     assert three == 3
     dev = gathered.device
-    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=dev)
     block = 3 * rows * k
     check(_lib.load().tlx_merge_and_sample(
         _stream(), gathered[0, 0].data_ptr(), gathered[0, 1].data_ptr(), gathered[0, 2].data_ptr(), rows,

@@ -54,14 +54,26 @@ def sample(rng_key, logits, tpu_sampling_metadata, *, noise=None, dim0_offset: i
                       dim0_offset=dim0_offset, workspace=workspace)
 
 
+class VocabShardedWorkspace:
+    """Preallocated buffers of `sample_vocab_sharded` (this rank's candidate block, the gathered blocks of all
+    ranks, the tokens), so that a decode loop allocates nothing per step."""
+
+    def __init__(self, rows: int, k_cand: int, world: int, device):
+        self.rows, self.k_cand, self.world = rows, k_cand, world
+        self.gathered = torch.empty((world, 3, rows, k_cand), dtype=torch.float32, device=device)
+        self.block = torch.empty((3, rows, k_cand), dtype=torch.float32, device=device)
+        self.tokens = torch.empty(rows, dtype=torch.int32, device=device)
+
+
 def sample_vocab_sharded(rng_key, logits_shard, tpu_sampling_metadata, *, group=None, noise_shard=None,
-                         k_cand: int | None = None, dim0_offset: int = 0):
+                         k_cand: int | None = None, dim0_offset: int = 0, workspace=None):
     """Sampler for logits sharded along the vocabulary across the ranks of `group`
     (the shard-mapped body of sampling.py:300-321): local top-k' on this rank's
     contiguous slice, one all-gather of the (value, global token, noise) candidates,
     then merge and sample.  Every rank returns the same tokens.
 
     Needs 1 <= top_k <= k_cand for every row (the reference fixes k' = 128).
+    One library call per stage; with `workspace` (a VocabShardedWorkspace) nothing is allocated.
     """
     import torch.distributed as dist
 
@@ -72,13 +84,16 @@ def sample_vocab_sharded(rng_key, logits_shard, tpu_sampling_metadata, *, group=
     if k_cand is None:
         k_cand = 128
     k_cand = min(k_cand, v_local)
-    block = ops.shard_candidates(logits_shard, rank * v_local, k_cand, noise_shard=noise_shard, rng_key=rng_key,
-                                 vocab_total=v_local * world, dim0_offset=dim0_offset)
-    gathered = torch.empty((world,) + tuple(block.shape), dtype=block.dtype, device=block.device)
+    w = workspace
+    if w is None:
+        w = VocabShardedWorkspace(rows, k_cand, world, logits_shard.device)
+    elif (w.rows, w.k_cand, w.world) != (rows, k_cand, world):
+        raise ValueError("workspace was made for another shape")
+    # a single rank writes its block straight into the gathered buffer
+    block = w.gathered[0] if world == 1 else w.block
+    ops.shard_candidates(logits_shard, rank * v_local, k_cand, noise_shard=noise_shard, rng_key=rng_key,
+                         vocab_total=v_local * world, dim0_offset=dim0_offset, out=block)
     if world > 1:
         # concatenated-along-dim-0 form: the one every backend accepts
-        dist.all_gather_into_tensor(gathered.view((world * block.shape[0],) + tuple(block.shape[1:])), block,
-                                    group=group)
-    else:
-        gathered[0].copy_(block)
-    return ops.merge_and_sample(gathered, md.top_k, md.top_p, md.temperature)
+        dist.all_gather_into_tensor(w.gathered.view((world * 3,) + tuple(block.shape[1:])), block, group=group)
+    return ops.merge_and_sample(w.gathered, md.top_k, md.top_p, md.temperature, out=w.tokens)

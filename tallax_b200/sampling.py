@@ -7,6 +7,7 @@ from tallax_b200._src.sampling import top_p_mask as top_p_mask
 from tallax_b200._src.sampling import top_p_and_sample as top_p_and_sample
 from tallax_b200._src.sampling import sample as sample
 from tallax_b200._src.sampling import sample_vocab_sharded as sample_vocab_sharded
+from tallax_b200._src.sampling import VocabShardedWorkspace as VocabShardedWorkspace
 from tallax_b200._src.sampling import SamplingMetadata as SamplingMetadata
 
-__all__ = ["top_p_mask", "top_p_and_sample", "sample", "sample_vocab_sharded", "SamplingMetadata"]
+__all__ = ["top_p_mask", "top_p_and_sample", "sample", "sample_vocab_sharded", "VocabShardedWorkspace", "SamplingMetadata"]

@@ -31,19 +31,23 @@ def _install_cpu_kernels():
                          dim0_offset=0, out=None):
         x = logits_shard.float().numpy()
         vals, idx, u = o.shard_candidates(x, col_offset, k_cand, noise_shard.numpy())
-        block = torch.empty((3,) + vals.shape, dtype=torch.float32)
+        block = out if out is not None else torch.empty((3,) + vals.shape, dtype=torch.float32)
         block[0] = torch.from_numpy(vals)
         block[1] = torch.from_numpy(idx.view(np.float32))   # token ids travel bit-cast in the f32 block
         block[2] = torch.from_numpy(u)
         return block
 
-    def merge_and_sample(gathered, top_k_, top_p, temperature):
+    def merge_and_sample(gathered, top_k_, top_p, temperature, out=None):
         n_shards, _, rows, k = gathered.shape
         g = gathered.numpy()
         cv = np.concatenate([g[s, 0] for s in range(n_shards)], axis=1)
         ci = np.concatenate([g[s, 1].view(np.int32) for s in range(n_shards)], axis=1)
         cn = np.concatenate([g[s, 2] for s in range(n_shards)], axis=1)
-        return torch.from_numpy(o.merge_and_sample(cv, ci, cn, top_k_.numpy(), top_p.numpy(), temperature.numpy()))
+        tok = torch.from_numpy(o.merge_and_sample(cv, ci, cn, top_k_.numpy(), top_p.numpy(), temperature.numpy()))
+        if out is not None:
+            out.copy_(tok)
+            return out
+        return tok
 
     ops.shard_candidates = shard_candidates
     ops.merge_and_sample = merge_and_sample
