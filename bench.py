@@ -312,11 +312,12 @@ def run_ours(args):
 
     # ---- the 256 rows split over the ranks (strong scaling): rank r samples rows [r*B/N, (r+1)*B/N) of ONE
     # global batch, its noise counters offset by dim0_offset = r*B/N, as the reference's batch sharding does
-    strong_ms = None
+    strong_ms, strong_mismatches = None, None
     if world > 1 and B % world == 0 and not args.rows_per_call:
         bl = B // world
         g_sets = [make_inputs(torch, device, seed=5000 + s) for s in range(N_SETS)]   # the same on every rank
         s_sets = [tuple(t[rank * bl:(rank + 1) * bl].contiguous() for t in gs[:4]) for gs in g_sets]
+        g0 = g_sets[0][:4]
         del g_sets
         s_ws = ops.SampleWorkspace(bl, V, device)
         s_meta = [sampling.SamplingMetadata(top_k=t[1], top_p=t[2], temperature=t[3]) for t in s_sets]
@@ -325,6 +326,14 @@ def run_ours(args):
             return sampling.sample(key, s_sets[i % N_SETS][0], s_meta[i % N_SETS], workspace=s_ws,
                                    dim0_offset=rank * bl)
 
+        # parity: the ranks' tokens, side by side, are the tokens of the unsharded call with the same key
+        mine = strong_step(0).clone()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        if rank == 0:
+            whole = sampling.sample(key, g0[0], sampling.SamplingMetadata(top_k=g0[1], top_p=g0[2], temperature=g0[3]))
+            strong_mismatches = int((torch.cat(parts) != whole).sum())
+        del g0
         for i in range(4):
             strong_step(i)
         barrier()
@@ -416,7 +425,7 @@ def run_ours(args):
         }
         if strong_ms:
             line["strong"] = {"rows_per_gpu": B // world, "ms_per_step": strong_ms, "value": B / (strong_ms / 1e3),
-                              "unit": UNIT, "scaling": "strong", "steps": 100,
+                              "unit": UNIT, "scaling": "strong", "steps": 100, "mismatches": strong_mismatches,
                               "note": "one global batch of 256 rows split over the ranks, dim0_offset = rank * rows_per_gpu, "
                                       "threefry noise from one key; max over ranks"}
         if vs:

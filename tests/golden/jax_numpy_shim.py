@@ -164,6 +164,7 @@ def install():
 
     pallas = types.ModuleType("jax.experimental.pallas")
     pallas.cdiv = lambda a, b: -(-a // b)
+    pallas.dslice = lambda start, size: slice(int(start), int(start) + int(size))   # a dynamic slice of an array
     pallas.pallas_call = _not_available
     pallas.BlockSpec = lambda *a, **k: None
     pallas.when = _not_available

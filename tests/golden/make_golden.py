@@ -112,6 +112,73 @@ def main(ref_root: str):
     out["cat_logits"], out["cat_rows"], out["cat_cols"] = lg, rws, cols
     out["cat_out0"], out["cat_out1"] = np.asarray(r[0]).astype(np.int32), np.asarray(r[1]).astype(np.int32)
 
+    # --- compare_and_swap: sort.py:39-102 ---------------------------------------------------------------
+    # (a) pairs of columns, key + payload, every direction form the function takes
+    from tallax._src.sort import compare_and_swap
+    kl = rng.integers(-4, 5, (4, 256)).astype(np.float32)          # small integers: many ties
+    kr = rng.integers(-4, 5, (4, 256)).astype(np.float32)
+    kl[0, :4] = [0.0, -0.0, 1.0, 2.0]
+    kr[0, :4] = [-0.0, 0.0, 1.0, 2.0]
+    pl_ = np.arange(4 * 256, dtype=np.int32).reshape(4, 256)        # payload = unique id, lefts below rights
+    pr_ = pl_ + 4 * 256
+    dyn = rng.integers(0, 2, (4, 256)).astype(np.int32)
+    out["cas_kl"], out["cas_kr"], out["cas_pl"], out["cas_pr"], out["cas_dyn"] = kl, kr, pl_, pr_, dyn
+    for name, nk, desc in (("asc1", 1, False), ("desc1", 1, True), ("asc2", 2, False), ("desc2", 2, True),
+                           ("dyn1", 1, J(dyn)), ("dyn2", 2, J(dyn))):
+        (ol_k, or_k), (ol_p, or_p) = compare_and_swap((J(kl), J(pl_)), (J(kr), J(pr_)), num_keys=nk, is_descending=desc)
+        out[f"cas_{name}_lk"], out[f"cas_{name}_rk"] = np.asarray(ol_k), np.asarray(or_k)
+        out[f"cas_{name}_lp"], out[f"cas_{name}_rp"] = np.asarray(ol_p), np.asarray(or_p)
+    # (b) a whole bitonic network over rows of 64 made of nothing but that comparator, keys (value, column)
+    n = 64
+    v = rng.integers(-6, 7, (8, n)).astype(np.float32)
+    v[1] = 3.0
+    v[2, ::2] = -0.0
+    v[2, 1::2] = 0.0
+    col = np.broadcast_to(np.arange(n, dtype=np.int32), (8, n)).copy()
+    for name, desc in (("asc", False), ("desc", True)):
+        a, b = v.copy(), col.copy()
+        size = 2
+        while size <= n:
+            stride = size // 2
+            while stride >= 1:
+                i = np.arange(n)
+                lo = i[(i & stride) == 0]
+                hi = lo | stride
+                up = ((lo & size) == 0)[None, :]                  # sub-sequence direction of the bitonic network
+                d = np.broadcast_to(up != (not desc), (8, len(lo))).astype(np.int32)   # 1 = descending pair
+                (la, ra), (lb, rb) = compare_and_swap((J(a[:, lo]), J(b[:, lo])), (J(a[:, hi]), J(b[:, hi])), num_keys=2,
+                                                      is_descending=J(d))
+                a[:, lo], a[:, hi], b[:, lo], b[:, hi] = np.asarray(la), np.asarray(ra), np.asarray(lb), np.asarray(rb)
+                stride //= 2
+            size *= 2
+        out[f"net_{name}_val"], out[f"net_{name}_col"] = a, b
+    out["net_in"] = v
+
+    # --- binned_top_k: top_k.py:13-106 (a ragged last slice; ties inside a bin) ------------------------------
+    from tallax._src.top_k import binned_top_k
+    kb, nb = 4, 128
+    xb = rng.integers(-20, 21, (4, 1000)).astype(np.float32)        # integers: ties inside most bins
+    xb[1] = rng.standard_normal(1000).astype(np.float32)
+    vals0 = [J(np.full((4, nb), np.finfo(np.float32).min, np.float32)) for _ in range(kb)]
+    idxs0 = [J(np.zeros((4, nb), np.int32)) for _ in range(kb)]
+    bv, bi = binned_top_k(J(xb), kb, vals0, idxs0, num_bins=nb)
+    out["binned_in"] = xb
+    out["binned_vals"] = np.stack([np.asarray(t) for t in bv])
+    out["binned_idxs"] = np.stack([np.asarray(t) for t in bi])
+
+    # --- pack_bf16_u16_to_i32 / unpack: utils.py:205-227 ------------------------------------------------------
+    import ml_dtypes
+    xp = (rng.integers(-8, 9, (4, 512)).astype(np.float32) * 0.5).astype(ml_dtypes.bfloat16)
+    xp[0, :4] = np.array([0.0, -0.0, 1.0, -1.0], np.float32).astype(ml_dtypes.bfloat16)
+    xp[3] = (rng.standard_normal(512).astype(np.float32) * 3).astype(ml_dtypes.bfloat16)
+    ip = np.broadcast_to(np.arange(512, dtype=np.int32), (4, 512)).copy()
+    packed = rutils.pack_bf16_u16_to_i32(J(xp), J(ip))
+    uv, ui = rutils.unpack_bf16_u16_from_i32(J(np.asarray(packed)))
+    out["pack_in"] = xp.astype(np.float32)    # bf16 values, stored as f32 (npz has no bf16)
+    out["pack_packed"] = np.asarray(packed).astype(np.int32)
+    out["pack_unpacked_val"] = np.asarray(uv).astype(np.float32)
+    out["pack_unpacked_idx"] = np.asarray(ui).astype(np.int32)
+
     path = os.path.join(HERE, "reference_value_level.npz")
     np.savez_compressed(path, **{k: np.asarray(v) for k, v in out.items()})
     print(f"wrote {path}: {len(out)} arrays, {os.path.getsize(path) / 1024:.0f} KiB")

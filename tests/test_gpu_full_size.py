@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import tallax_oracle as o
 from tallax_b200 import sampling, tax, tumpy
 from tallax_b200._src import ops
 
@@ -56,5 +57,13 @@ def test_vocab_sharded_equals_unsharded_configuration_5(cuda):
     merged = ops.merge_and_sample(torch.stack(blocks), md.top_k, md.top_p, md.temperature)
     # The two paths take the softmax over the same top-k set in different summation orders, so a row
     # whose cumulative mass sits within rounding of top_p may differ; everything else is identical.
-    assert (whole != merged).float().mean().item() <= 2.0 / rows
+    differing = torch.nonzero(whole != merged).flatten().tolist()
+    assert len(differing) <= 2
+    if differing:
+        # every such row must be one the oracle flags: cumulative mass within 1e-6 of top_p
+        from tests.conftest import to_np
+        n = len(differing)
+        _, flags = o.sample(to_np(x[differing]), np.full(n, k, np.int32), np.full(n, 0.95, np.float32),
+                            np.full(n, 0.8, np.float32), noise=to_np(noise[differing]), return_flags=True)
+        assert flags.all(), (differing, flags)
     assert int(whole.min()) >= 0 and int(whole.max()) < vocab
