@@ -55,6 +55,13 @@ unsigned long long tlx_kernel_launches(void);
 #define TLX_INIT_SIDE_STREAM 1u
 int tlx_init(int device, unsigned flags);
 
+/* Checked builds only (python -m tallax_b200.build --checked -> libtallax_b200_checked.so): the streaming
+ * sampler's kernels verify the shared-memory and workspace indices they rely on, skip an access whose index
+ * is out of range and record the first such event.  Synchronises the device, copies {violations, site,
+ * index, bound} to out4 (nullable), clears the record, and returns 1 if there was a violation, 0 if not;
+ * TLX_ERR_UNSUPPORTED in other builds.                                                               */
+int tlx_debug_check_status(int32_t* out4);
+
 /* ---- device operands -------------------------------------------------------------------------
  * A caller under a tracing compiler (an XLA custom call, a CUDA graph whose key changes between
  * replays) has the PRNG key and the batch offset only as device buffers.  The *_dev entry points

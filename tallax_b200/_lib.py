@@ -23,6 +23,7 @@ SIGNATURES = {
     "tlx_last_error": (C.c_char_p, []),
     "tlx_kernel_launches": (C.c_ulonglong, []),
     "tlx_init": (_i32, [_i32, _u32]),
+    "tlx_debug_check_status": (_i32, [_vp]),
     "tlx_take_along_axis": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32]),
     "tlx_cumsum": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32]),
     "tlx_argmax": (_i32, [_vp, _vp, _i32, _i64, _i64, _i32, _vp]),
@@ -67,10 +68,13 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
+    path = LIB_PATH
+    if os.environ.get("TLX_LIBRARY") == "checked":   # the index-checking build (python -m tallax_b200.build --checked)
+        path = os.path.join(os.path.dirname(LIB_PATH), "libtallax_b200_checked.so")
+    if not os.path.exists(path):
         raise TallaxLibraryError(
-            f"{LIB_PATH} is missing: build it with `python -m tallax_b200.build`; there is no CPU or PyTorch fallback")
-    lib = C.CDLL(LIB_PATH)
+            f"{path} is missing: build it with `python -m tallax_b200.build`; there is no CPU or PyTorch fallback")
+    lib = C.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if the library does not export a declared symbol
         fn.restype = res

@@ -3,7 +3,9 @@
     python -m tallax_b200.build            # recompile the sources that changed, then link
     python -m tallax_b200.build --force    # recompile everything
     python -m tallax_b200.build -v         # print ptxas resource usage (registers, spills, shared memory)
-    python -m tallax_b200.build --checked  # bounds-checked build (see tlx_common.cuh, TLX_CHECKED)
+    python -m tallax_b200.build --checked  # libtallax_b200_checked.so: the streaming sampler verifies its
+                                           # indices (tlx_common.cuh, TLX_IN_BOUNDS); loaded instead of the
+                                           # normal library when TLX_LIBRARY=checked is set
     python -m tallax_b200.build --timeline # libtallax_b200_timeline.so: the streaming sampler's kernels
                                            # record global-timer stamps per CTA (sampler.cu, TLX_STAMP)
 
@@ -58,7 +60,9 @@ def build(force: bool = False, verbose: bool = False, checked: bool = False, tim
     obj_dir, lib_path = OBJ_DIR, LIB_PATH
     if checked:
         flags += ["-DTLX_CHECKED=1"]
-        tag = ".checked"
+        obj_dir = os.path.join(LIB_DIR, "obj_checked")
+        lib_path = os.path.join(LIB_DIR, "libtallax_b200_checked.so")
+        os.makedirs(obj_dir, exist_ok=True)
     if timeline:
         flags += ["-DTLX_TIMELINE=1"] + (["-DTLX_TIMELINE_TWICE=1"] if os.environ.get("TLX_TIMELINE_TWICE") else [])
         obj_dir = os.path.join(LIB_DIR, "obj_timeline")

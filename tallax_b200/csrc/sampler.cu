@@ -2280,6 +2280,21 @@ static int sample_impl(void* stream, const void* logits, int dtype, int64_t rows
   return TLX_OK;
 }
 
+int tlx_debug_check_status(int32_t* out4) {
+#ifdef TLX_CHECKED
+  int32_t w[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpyFromSymbol(w, g_tlx_check_word, sizeof(w)) != cudaSuccess)
+    return set_error(TLX_ERR_CUDA, "debug_check_status: could not read the check word");
+  const int32_t zero[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(g_tlx_check_word, zero, sizeof(zero));
+  if (out4) for (int i = 0; i < 4; ++i) out4[i] = w[i];
+  return w[0] ? 1 : 0;
+#else
+  if (out4) for (int i = 0; i < 4; ++i) out4[i] = 0;
+  return set_error(TLX_ERR_UNSUPPORTED, "debug_check_status: not a checked build (python -m tallax_b200.build --checked)");
+#endif
+}
+
 int tlx_init(int device, unsigned flags) {
   int count = 0;
   if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)

@@ -408,7 +408,7 @@ __device__ __forceinline__ void st_filter_chunk(const unsigned char* buf, int nv
     }
     const uint32_t mask = __ballot_sync(0xFFFFFFFFu, hit);
     if (mask) {
-      if (hit) wl[wn + __popc(mask & lt)] = (unsigned short)v;
+      if (hit && TLX_IN_BOUNDS(wn + __popc(mask & lt), 32 * kStVecPerThread, 1)) wl[wn + __popc(mask & lt)] = (unsigned short)v;
       wn += __popc(mask);
     }
   }
@@ -420,8 +420,8 @@ __device__ __forceinline__ void st_filter_chunk(const unsigned char* buf, int nv
     uint32_t entry = 0;
     if (e < wn) {
       const int q = wl[e] * 8 + (lane & 7);
-      const uint32_t bits = reinterpret_cast<const unsigned short*>(buf)[q];
-      pass = !(__uint_as_float(bits << 16) < tvf);
+      const uint32_t bits = TLX_IN_BOUNDS(q, kStChunkElems, 2) ? reinterpret_cast<const unsigned short*>(buf)[q] : 0u;
+      pass = !(__uint_as_float(bits << 16) < tvf) && TLX_IN_BOUNDS(pos0 + q, 65536, 3);   // positions are 16 bits
       entry = (bits << 16) | (uint32_t)(pos0 + q);
     }
     const uint32_t pm = __ballot_sync(0xFFFFFFFFu, pass);
@@ -665,7 +665,8 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         total += ctl.ibest[w];
         if (pass == 0) nwide_first += ctl.wtok[w];
       }
-      if (take) order_rows[off + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)r;
+      if (take && TLX_IN_BOUNDS(off + __popc(mask & ((1u << lane) - 1u)), rows, 10))
+        order_rows[off + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)r;
       nlisted += total;
       __syncthreads();
     }
@@ -775,7 +776,7 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         if (mine) {
           FinRecord r;
           r.a = a1; r.u = u1; r.tok = any ? t1 : 0x7FFFFFFF; r.bits = b1 | (multi ? 0x10000u : 0u);
-          p.records[(size_t)row * p.nfin + part] = r;
+          if (TLX_IN_BOUNDS(part, p.nfin, 8) && TLX_IN_BOUNDS(row, rows, 9)) p.records[(size_t)row * p.nfin + part] = r;
           if (any) atomicMax(&p.wstate[row].best_key, bkey);
         }
       }
@@ -783,7 +784,7 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
       if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + 3;
       continue;
     }
-    const uint32_t dw = dtab[row];
+    const uint32_t dw = TLX_IN_BOUNDS(row, rows, 7) ? dtab[row] : ((uint32_t)kStOther << 16);
     const int cls = (int)(dw >> 16), key16 = (int)(dw & 0xFFFFu);
     const int c0 = part * p.part_chunks;
     const int nc = st_part_chunks(p, part);
@@ -918,6 +919,7 @@ __device__ __forceinline__ void tl_place(TailShared& t, const StreamParams& p, c
   const uint32_t k16 = bf16_key16(e >> 16);
   const int bin = (int)k16 - d.key16;
   const uint32_t tok = (uint32_t)(sg / kStWarps) * (uint32_t)(p.part_chunks * kStChunkElems) + (e & 0xFFFFu);
+  if (!TLX_IN_BOUNDS(f, kMergeCap, 4) || !TLX_IN_BOUNDS(tok, p.sp.vocab, 5)) return;
   t.tok[f] = tok;
   t.key[f] = (unsigned short)k16;
   if (noise_row) prefetch_l2(noise_row + tok);   // most candidates' noise is wanted a few microseconds from now
@@ -1124,7 +1126,10 @@ __device__ __forceinline__ int st_finish_normal(const StreamParams& p, int row, 
     __syncthreads();
 #pragma unroll 1
     for (int f = threadIdx.x; f < m; f += kStThreads)
-      if (kmax16 - (int)t.key[f] == vk_idx) tie_tok[atomicAdd(&t.nties, 1)] = t.tok[f];
+      if (kmax16 - (int)t.key[f] == vk_idx) {
+        const int slot = atomicAdd(&t.nties, 1);
+        if (TLX_IN_BOUNDS(slot, kTlBins, 6)) tie_tok[slot] = t.tok[f];
+      }
     __syncthreads();
     const int nties = t.nties;
 #pragma unroll 1

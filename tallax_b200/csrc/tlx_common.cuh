@@ -223,6 +223,28 @@ __device__ __forceinline__ float gumbel_screen(float u) {
 }
 constexpr float kGumbelSlack = 1e-3f;
 
+// ---- checked build ------------------------------------------------------------------------------
+// python -m tallax_b200.build --checked compiles with TLX_CHECKED: TLX_IN_BOUNDS(i, n, site) then tests an
+// index that the code relies on being in range (it is false, and the access is skipped, when it is not) and
+// records the first violation in a device word that tlx_debug_check_status reads.  In other builds the
+// macro is the constant `true` and costs nothing.  It stands in for a memory checker where none can be
+// run; the sites are the shared-memory and workspace indices of the streaming sampler.
+#ifdef TLX_CHECKED
+static __device__ int g_tlx_check_word[4];   // violations so far; site, index and bound of the first
+__device__ __forceinline__ bool tlx_check_fail(int site, long long i, long long n) {
+  if (atomicAdd(&g_tlx_check_word[0], 1) == 0) {
+    g_tlx_check_word[1] = site;
+    g_tlx_check_word[2] = (int)i;
+    g_tlx_check_word[3] = (int)n;
+  }
+  return false;
+}
+#define TLX_IN_BOUNDS(i, n, site) \
+  (((unsigned long long)(long long)(i) < (unsigned long long)(long long)(n)) || tlx_check_fail((site), (long long)(i), (long long)(n)))
+#else
+#define TLX_IN_BOUNDS(i, n, site) true
+#endif
+
 // Noise source shared by the samplers: dense tensor or threefry key.
 // The key and the row offset may also be given as device operands (the *_dev entry points): the key as
 // two words in device memory, the offset as an int32 scalar in device memory that is added to every row

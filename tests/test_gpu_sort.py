@@ -97,3 +97,15 @@ def test_tumpy_sort_and_argsort(cuda):
     assert np.array_equal(to_np(flat), np.sort(a.ravel(), kind="stable"))
     with pytest.raises(ValueError):
         tumpy.sort(to_dev(a, cuda), axis=1)
+
+
+@pytest.mark.parametrize("size", [1 << 19, (1 << 19) + 12345])
+def test_sort_rows_beyond_two_to_the_18(cuda, size):
+    # the regime of the reference's HBM-resident merge stages (sort.py:588-758, 860-900): rows that no
+    # shared-memory tile holds, sorted by the library's multi-pass path
+    rng = np.random.default_rng(7)
+    keys = rng.standard_normal((2, size)).astype(np.float32)
+    keys[1] = np.round(keys[1] * 4) / 4          # many ties: the stable order among them is checked
+    pay = rng.integers(0, 1 << 30, (2, size)).astype(np.int32)
+    _check(cuda, [keys, pay], 1, "return_argsort_stable")
+    _check(cuda, [keys.astype(o.bfloat16)], 1, "descending_argsort")
