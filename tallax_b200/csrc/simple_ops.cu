@@ -22,34 +22,48 @@ void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 // ---------------------------------------------------------------------------------
 // gather
 // ---------------------------------------------------------------------------------
+// Eight consecutive outputs per thread: two 16-byte index loads, eight independent random reads in flight,
+// 16-byte stores.  The random reads are what the kernel waits for (a 32-byte DRAM sector per element), so
+// the number a thread keeps in flight is what sets the rate.
 template <typename T>
-__global__ void gather_axis1_kernel(const T* __restrict__ values, const int32_t* __restrict__ idx,
-                                    T* __restrict__ out, int64_t rows, int64_t vcols, int64_t icols) {
-  // 4 consecutive outputs per thread: one 16-byte index load when aligned.
-  const int64_t quads_per_row = (icols + 3) >> 2;
-  const int64_t total = rows * quads_per_row;
-  for (int64_t q = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; q < total;
-       q += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = q / quads_per_row;
-    const int64_t c0 = (q - r * quads_per_row) << 2;
+__global__ void __launch_bounds__(256) gather_axis1_kernel(const T* __restrict__ values, const int32_t* __restrict__ idx,
+                                                           T* __restrict__ out, int64_t rows, int64_t vcols, int64_t icols) {
+  constexpr int kPer = 8;
+  const int64_t groups_per_row = (icols + kPer - 1) / kPer;
+  const int64_t total = rows * groups_per_row;
+  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = g / groups_per_row;
+    const int64_t c0 = (g - r * groups_per_row) * kPer;
     const int32_t* ip = idx + r * icols + c0;
     const T* vrow = values + r * vcols;
     T* op = out + r * icols + c0;
-    int32_t i4[4];
-    const int n = (int)min((int64_t)4, icols - c0);
-    if (n == 4 && ((reinterpret_cast<uintptr_t>(ip) & 15) == 0)) {
-      int4 v = __ldg(reinterpret_cast<const int4*>(ip));
-      i4[0] = v.x; i4[1] = v.y; i4[2] = v.z; i4[3] = v.w;
+    int32_t ii[kPer];
+    const int n = (int)min((int64_t)kPer, icols - c0);
+    if (n == kPer && ((reinterpret_cast<uintptr_t>(ip) & 15) == 0)) {
+      const int4 a = __ldcs(reinterpret_cast<const int4*>(ip));
+      const int4 b = __ldcs(reinterpret_cast<const int4*>(ip) + 1);
+      ii[0] = a.x; ii[1] = a.y; ii[2] = a.z; ii[3] = a.w;
+      ii[4] = b.x; ii[5] = b.y; ii[6] = b.z; ii[7] = b.w;
     } else {
-      for (int j = 0; j < 4; ++j) i4[j] = (j < n) ? __ldg(ip + j) : -1;
-    }
-    T o[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const bool ok = (j < n) && i4[j] >= 0 && (int64_t)i4[j] < vcols;
-      o[j] = ok ? __ldg(vrow + i4[j]) : T(0);
+      for (int j = 0; j < kPer; ++j) ii[j] = (j < n) ? __ldg(ip + j) : -1;
     }
-    for (int j = 0; j < n; ++j) op[j] = o[j];
+    T o[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const bool ok = (j < n) && ii[j] >= 0 && (int64_t)ii[j] < vcols;
+      o[j] = ok ? __ldg(vrow + ii[j]) : T(0);
+    }
+    if (n == kPer && sizeof(T) == 4 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+      uint4 w0, w1;
+      memcpy(&w0, &o[0], 16);
+      memcpy(&w1, &o[4], 16);
+      __stcs(reinterpret_cast<uint4*>(op), w0);
+      __stcs(reinterpret_cast<uint4*>(op) + 1, w1);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) if (j < n) op[j] = o[j];
+    }
   }
 }
 
@@ -71,10 +85,10 @@ static int launch_gather(cudaStream_t st, const void* values, const int32_t* idx
                          int64_t vc, int64_t ir, int64_t ic, int axis) {
   const int threads = 256;
   if (axis == 1) {
-    const int64_t total = ir * ((ic + 3) >> 2);
+    const int64_t total = ir * ((ic + 7) >> 3);
     if (total == 0) return TLX_OK;
     const int64_t want = (total + threads - 1) / threads;
-    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    const int blocks = (int)(want < 148 * 64 ? want : 148 * 64);
     gather_axis1_kernel<T><<<blocks, threads, 0, st>>>((const T*)values, idx, (T*)out, ir, vc, ic);
   } else {
     const int64_t total = ir * ic;

@@ -3,6 +3,8 @@
 // the top-k in shared memory, a bitonic network orders it by (value desc, index asc).
 #include "select.cuh"
 
+#include <mutex>
+
 namespace tlx {
 
 constexpr int kTopkThreads = 512;
@@ -92,14 +94,28 @@ __global__ void __launch_bounds__(kTopkThreads) topk_kernel(TopkParams p) {
   }
 }
 
-__global__ void set_int_kernel(int32_t* p, int32_t v) { *p = v; }
-
 template <int DT, int CAP>
 static int launch_topk_cap(cudaStream_t st, const TopkParams& p) {
   const size_t smem = ((sizeof(SelectShared) + 15) & ~size_t(15)) + (size_t)CAP * 8;
-  cudaError_t e = cudaFuncSetAttribute(topk_kernel<DT, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "top_k: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  if (p.out_valid) set_int_kernel<<<1, 1, 0, st>>>(p.out_valid, 1);
+  // the shared-memory limit of this instantiation is raised once per device, not per call
+  static std::mutex mu;
+  static bool raised[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !raised[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(topk_kernel<DT, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "top_k: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      if (dev >= 0 && dev < 64) raised[dev] = true;
+    }
+  }
+  // out_valid starts as 1: a stream-ordered 4-byte copy node instead of a kernel of its own
+  if (p.out_valid) {
+    static const int32_t one = 1;
+    cudaError_t e = cudaMemcpyAsync(p.out_valid, &one, sizeof(one), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "top_k: cudaMemcpyAsync: %s", cudaGetErrorString(e));
+  }
   topk_kernel<DT, CAP><<<(unsigned)p.rows, kTopkThreads, smem, st>>>(p);
   TLX_CHECK_LAUNCH("top_k");
   return TLX_OK;
