@@ -883,6 +883,7 @@ struct __align__(16) TailShared {
   uint32_t hist[kTlBins];          // candidates per key, bin = key16 - threshold key
   uint32_t tok[kMergeCap];         // the candidates' tokens ...
   unsigned short key[kMergeCap];   // ... and keys
+  uint32_t raw[kTlSegs * kStSpec]; // the segments' first kStSpec entries as fetched (32 slots per segment)
   int segcnt[kTlSegs];
   int segoff[kTlSegs];             // exclusive offsets of the segments
   uint32_t scan_c[kStWarps];
@@ -968,7 +969,12 @@ __device__ __forceinline__ int st_finish_normal(const StreamParams& p, int row, 
   const uint32_t* cbase = p.cands + (size_t)row * nseg * kStWarpCap;
   const int sg = (int)threadIdx.x / kSubs, sub = (int)threadIdx.x % kSubs;
   const int cnt = fetched.cnt;
-  if (sg < nseg && sub == 0) t.segcnt[sg] = cnt;
+  if (sg < nseg) {
+    if (sub == 0) t.segcnt[sg] = cnt;
+    uint4* rv = reinterpret_cast<uint4*>(t.raw) + sg * (kStSpec / 4) + sub;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) rv[q * kSubs] = fetched.e[q];
+  }
   if (threadIdx.x == 0) { t.maxbin = 0; t.overflow = 0; t.nties = 0; }
   __syncthreads();
   // ---- the segments' offsets (warp 0: four segments per lane)
@@ -1004,22 +1010,20 @@ __device__ __forceinline__ int st_finish_normal(const StreamParams& p, int row, 
   // ---- candidates: tokens and keys to shared memory, keys into the histogram
   {
     int mymax = 0, over = 0;
-    if (sg < nseg) {
-      const int f0 = t.segoff[sg];
-      // rolled on purpose (as are the loops below): this code runs once per CTA, so the time goes into
-      // fetching its instructions, not into executing them
+    // The fetched slots, dealt evenly to the threads (a slot is an entry if its index is below its segment's
+    // count).  Rolled on purpose, as are the loops below: this code runs once per CTA, so the time goes into
+    // fetching its instructions, not into executing them.
 #pragma unroll 1
-      for (int i = 0; i < 16; ++i) {
-        const int q = i >> 2, k = i & 3;
-        const uint4 v = q == 0 ? fetched.e[0] : q == 1 ? fetched.e[1] : q == 2 ? fetched.e[2] : fetched.e[3];
-        const uint32_t w = k == 0 ? v.x : k == 1 ? v.y : k == 2 ? v.z : v.w;
-        const int idx = (sub + q * kSubs) * 4 + k;
-        if (idx >= cnt) break;
-        tl_place(t, p, d, noise_row, w, sg, f0 + idx, mymax, over);
-      }
-      // what a segment holds beyond the entries fetched ahead
-      for (int idx = kStSpec + sub; idx < cnt; idx += kSubs)
-        tl_place(t, p, d, noise_row, __ldcg(cbase + (size_t)sg * kStWarpCap + idx), sg, f0 + idx, mymax, over);
+    for (int i = threadIdx.x; i < nseg * kStSpec; i += kStThreads) {
+      const int s2 = i / kStSpec, idx = i % kStSpec;
+      if (idx < t.segcnt[s2]) tl_place(t, p, d, noise_row, t.raw[i], s2, t.segoff[s2] + idx, mymax, over);
+    }
+    // what a segment holds beyond the entries fetched ahead: a warp per such segment
+#pragma unroll 1
+    for (int s2 = warp; s2 < nseg; s2 += kStWarps) {
+      const int c = t.segcnt[s2];
+      for (int idx = kStSpec + lane; idx < c; idx += 32)
+        tl_place(t, p, d, noise_row, __ldcg(cbase + (size_t)s2 * kStWarpCap + idx), s2, t.segoff[s2] + idx, mymax, over);
     }
     mymax = __reduce_max_sync(0xFFFFFFFFu, mymax);
     if (lane == 0) atomicMax(&t.maxbin, mymax);
