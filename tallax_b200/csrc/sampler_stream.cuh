@@ -710,6 +710,8 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         // all claimed before this one, by CTAs that wait for nothing but their copies, so the wait is
         // short; it is bounded all the same.
         volatile int* rp = &p.wstate[row].result;
+        const float T_ = p.sp.temperature[row];                                             // one round trip
+        const uint32_t bk = *reinterpret_cast<volatile uint32_t*>(&p.wstate[row].best_key);  // for all three
         int res = *rp;
         for (int spin = 0; res == kWideNotReady && spin < (1 << 16); ++spin) {
           __nanosleep(64);
@@ -717,8 +719,8 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         }
         if (res == kWideNotReady) { *p.error_flag = 1; res = -1; }
         ctl.fin_result = res;
-        ctl.best_key = *reinterpret_cast<volatile uint32_t*>(&p.wstate[row].best_key);
-        ctl.fin_T = p.sp.temperature[row];
+        ctl.best_key = bk;
+        ctl.fin_T = T_;
       }
       __syncthreads();
       const int res = ctl.fin_result;
