@@ -164,10 +164,13 @@ def top_k(x: torch.Tensor, k_max: int, k_per_row=None, replace_val=None, single_
         valid = torch.empty(1, dtype=torch.int32, device=dev)
         depths = torch.empty(rows, dtype=torch.int32, device=dev)
         cutoff = torch.empty(rows, dtype=torch.int32 if x.dtype == torch.int32 else torch.float32, device=dev)
-    check(_lib.load().tlx_top_k(_stream(), _ptr(x), dtype_code(x), rows, n, n, int(k_max), _ptr(kpr),
-                                int(kpr is not None), float(replace_val if replace_val is not None else 0.0),
-                                int(single_pass), _ptr(vals), _ptr(idx), _ptr(valid), _ptr(depths), _ptr(cutoff), None,
-                                0))
+    lib = _lib.load()
+    ws_bytes = 0 if single_pass else lib.tlx_top_k_workspace_bytes(rows, n, int(k_max))   # a few long rows: split over CTAs
+    ws = _ws(ws_bytes, dev) if ws_bytes else None
+    check(lib.tlx_top_k(_stream(), _ptr(x.contiguous()), dtype_code(x), rows, n, n, int(k_max), _ptr(kpr),
+                        int(kpr is not None), float(replace_val if replace_val is not None else 0.0),
+                        int(single_pass), _ptr(vals), _ptr(idx), _ptr(valid), _ptr(depths), _ptr(cutoff), _ptr(ws),
+                        ws.numel() if ws is not None else 0))
     if single_pass:
         return vals, idx, valid, depths, cutoff
     return vals, idx

@@ -139,17 +139,58 @@ static int dispatch_topk(cudaStream_t st, int dtype, const TopkParams& p, const 
   }
 }
 
+// ---- a handful of long rows: every row is cut into parts, each part's top-k is found by a CTA of its own
+// (the same kernel on rows * parts "rows"), and a second pass takes the top-k of the parts' candidates.
+// Among equal values the parts' order and, inside a part, the ascending index order of its candidates keep
+// the lower original index first, as the one-pass kernel does.
+struct SplitPlan {
+  int parts = 0;          // 0: no split
+  int64_t part_len = 0;
+  size_t off_idx_a = 0, off_idx_b = 0, bytes = 0;
+};
+
+static SplitPlan split_plan(int64_t rows, int64_t n, int k_max, int elem_bytes) {
+  SplitPlan sp;
+  if (rows <= 0 || rows > 16 || n < 16384 || k_max > 256) return sp;   // more rows fill the GPU by themselves
+  for (int parts = 16; parts >= 4; parts >>= 1) {
+    if (n % parts) continue;
+    const int64_t len = n / parts;
+    if (len < 2048 || len < 4 * (int64_t)k_max || (len * elem_bytes) % 16) continue;
+    sp.parts = parts;
+    sp.part_len = len;
+    break;
+  }
+  if (!sp.parts) return sp;
+  auto align = [](size_t v) { return (v + 255) & ~size_t(255); };
+  const size_t cand = (size_t)rows * sp.parts * k_max;
+  sp.off_idx_a = align(cand * elem_bytes);
+  sp.off_idx_b = sp.off_idx_a + align(cand * 4);
+  sp.bytes = sp.off_idx_b + align((size_t)rows * k_max * 4);
+  return sp;
+}
+
+// out_idx[r, j] = original column of the candidate that the second pass picked at position pos_b[r, j]
+__global__ void topk_map_index_kernel(const int32_t* __restrict__ idx_a, const int32_t* __restrict__ pos_b,
+                                      int32_t* __restrict__ out_idx, int64_t rows, int k, int parts, int64_t part_len) {
+  const int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (e >= rows * k) return;
+  const int64_t r = e / k;
+  const int pos = pos_b[e];
+  out_idx[e] = idx_a[r * (int64_t)parts * k + pos] + (int32_t)((pos / k) * part_len);
+}
+
 }  // namespace tlx
 
 using namespace tlx;
 
 extern "C" {
 
-size_t tlx_top_k_workspace_bytes(int64_t, int64_t, int) { return 0; }
+size_t tlx_top_k_workspace_bytes(int64_t rows, int64_t n, int k_max) { return split_plan(rows, n, k_max, 4).bytes; }
 
 int tlx_top_k(void* stream, const void* x, int dtype, int64_t rows, int64_t n, int64_t row_stride, int k_max,
               const int32_t* k_per_row, int use_replace, double replace_val, int mode, void* out_vals,
-              int32_t* out_idx, int32_t* out_valid, int32_t* out_depths, void* out_cutoff, void*, size_t) {
+              int32_t* out_idx, int32_t* out_valid, int32_t* out_depths, void* out_cutoff, void* workspace,
+              size_t workspace_bytes) {
   cudaStream_t st = (cudaStream_t)stream;
   TLX_CHECK_ARG(rows >= 0 && n >= 0, "top_k: negative extent");
   TLX_CHECK_ARG(k_max >= 1, "top_k: k must be >= 1, got %d", k_max);
@@ -161,6 +202,30 @@ int tlx_top_k(void* stream, const void* x, int dtype, int64_t rows, int64_t n, i
   TLX_CHECK_ARG(row_stride >= n, "top_k: row stride smaller than the row");
   if (rows == 0) return TLX_OK;
   TLX_CHECK_ARG(x && out_vals && out_idx, "top_k: null pointer");
+  // few long rows, exact mode, no diagnostics asked for, and scratch given: split the rows over CTAs
+  const int es = dtype == TLX_BF16 || dtype == TLX_F16 ? 2 : 4;
+  const SplitPlan sp = split_plan(rows, n, k_max, es);
+  if (sp.parts && mode == 0 && !out_valid && !out_depths && !out_cutoff && row_stride == n && workspace &&
+      workspace_bytes >= sp.bytes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    unsigned char* ws = (unsigned char*)workspace;
+    TopkParams a{};
+    a.x = x; a.rows = rows * sp.parts; a.n = sp.part_len; a.row_stride = sp.part_len; a.k_max = k_max;
+    a.out_vals = ws; a.out_idx = (int32_t*)(ws + sp.off_idx_a);
+    int rc = dispatch_topk(st, dtype, a, "top_k");
+    if (rc != TLX_OK) return rc;
+    TopkParams b{};
+    b.x = ws; b.rows = rows; b.n = (int64_t)sp.parts * k_max; b.row_stride = b.n; b.k_max = k_max;
+    b.k_per_row = k_per_row; b.use_replace = use_replace; b.replace_val = replace_val;
+    b.out_vals = out_vals; b.out_idx = (int32_t*)(ws + sp.off_idx_b);
+    if ((rc = dispatch_topk(st, dtype, b, "top_k")) != TLX_OK) return rc;
+    const int64_t total = rows * k_max;
+    topk_map_index_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const int32_t*)(ws + sp.off_idx_a),
+                                                                          (const int32_t*)(ws + sp.off_idx_b), out_idx, rows,
+                                                                          k_max, sp.parts, sp.part_len);
+    TLX_CHECK_LAUNCH("top_k (index map)");
+    return TLX_OK;
+  }
   TopkParams p{};
   p.x = x; p.rows = rows; p.n = n; p.row_stride = row_stride; p.k_max = k_max; p.k_per_row = k_per_row;
   p.use_replace = use_replace; p.replace_val = replace_val; p.mode = mode; p.out_vals = out_vals;

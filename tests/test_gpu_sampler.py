@@ -269,3 +269,24 @@ def test_merge_and_sample_with_more_than_1024_candidates(cuda, top_k):
                                    noise_shard=dn[:, s * vl:(s + 1) * vl].contiguous()) for s in range(n_shards)]
     got = ops.merge_and_sample(torch.stack(blocks), to_dev(tk, cuda), to_dev(tp, cuda), to_dev(T, cuda))
     _assert_tokens(to_np(got), exp, flags, min_checked=0.7)
+
+
+@pytest.mark.parametrize("dtype,v_local,k", [("bf16", 18992, 50), ("f32", 20000, 128), ("bf16", 37984, 50), ("bf16", 700, 50)])
+def test_shard_candidates_of_many_short_rows(cuda, dtype, v_local, k):
+    # the shard's top-k by (value desc, index asc), global token ids, the noise at those tokens, on rows that
+    # defeat a sampled threshold (one value only, ascending, fewer finite values than k, NaNs)
+    B = 300
+    x, _, _, _, noise = o.make_sharded_inputs(B=B, V=v_local, seed=12, dtype=dtype)
+    xf = x.astype(np.float32)
+    xf[0] = 1.5                                        # one value only: a tie group larger than any list
+    xf[1] = np.round(xf[1])                            # heavy ties around the k-th value
+    xf[2] = np.arange(v_local, dtype=np.float32) / 64   # ascending: the sample sees only the smallest elements
+    xf[3] = -np.arange(v_local, dtype=np.float32) / 64  # descending
+    xf[4, 40:] = -np.inf                               # fewer finite values than k
+    xf[5, ::3] = np.nan
+    x = xf.astype(x.dtype)
+    ev, ei, en = o.shard_candidates(x, 1000, k, noise)
+    got = ops.shard_candidates(to_dev(x, cuda), 1000, k, noise_shard=to_dev(noise, cuda))
+    gv, gi, gn = to_np(got[0]), to_np(got[1].view(torch.int32)), to_np(got[2])
+    assert np.array_equal(gi, ei)
+    assert np.array_equal(gv, ev, equal_nan=True) and np.array_equal(gn, en)

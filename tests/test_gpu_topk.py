@@ -100,3 +100,29 @@ def test_single_pass_topk_contract(cuda):
     assert not bool(valid)
     ii = to_np(i)
     assert ii.min() >= 0 and ii.max() < 100000 and all(len(set(r.tolist())) == 64 for r in ii)
+
+
+@pytest.mark.parametrize("rows,n,k,dtype", [(8, 32768, 64, "f32"), (3, 65536, 256, "f32"), (16, 32768, 128, "bf16"),
+                                             (1, 131072, 17, "f32"), (5, 49152, 50, "i32")])
+def test_topk_of_a_few_long_rows_split_over_ctas(cuda, rows, n, k, dtype):
+    # the rows are cut into parts whose candidates a second pass merges; ties across and inside parts must
+    # still come out with the lower index first
+    from tallax_b200 import _lib
+    assert _lib.load().tlx_top_k_workspace_bytes(rows, n, k) > 0       # this shape does take the split path
+    rng = np.random.default_rng(rows * 1000 + k)
+    if dtype == "i32":
+        x = rng.integers(-50, 51, (rows, n)).astype(np.int32)
+    else:
+        x = np.round(rng.standard_normal((rows, n)).astype(np.float32) * 8) / 8      # eighths: plenty of ties
+        x[0, ::4096] = 7.0                                                           # a tie group across all parts
+        if rows > 1:
+            x[1] = -3.0                                                              # one value only
+        if dtype == "bf16":
+            x = x.astype(o.bfloat16)
+    _check_topk(cuda, x, k)
+    if dtype == "f32":
+        kk = rng.integers(1, k + 1, rows).astype(np.int32)
+        v, i = tax.top_dynamic_k(to_dev(x, cuda), to_dev(kk, cuda), max_k=k, replace_val=-1e12, block_token=1,
+                                 guarantee_convergence=True)
+        ev, ei = o.top_dynamic_k(x, kk, k, replace_val=-1e12)
+        assert exact_match(to_np(v), ev) and np.array_equal(to_np(i), ei)
