@@ -137,6 +137,10 @@ int tlx_sort_static(void* stream, const void* keys, int dtype, int64_t rows, int
  * seen, out_valid[0] is cleared, out_depths[row] is the number of threshold
  * refinements and out_cutoff[row] (f32 for float input, i32 for int) the final
  * candidate threshold.  out_valid/out_depths/out_cutoff may be NULL in mode 0.
+ * workspace (optional): with tlx_top_k_workspace_bytes(rows, n, k_max) bytes of scratch (non-zero
+ * only for up to 16 rows of at least 16 384 elements) an exact call that asks for no diagnostics
+ * cuts every row into parts, one CTA each, and merges the parts' candidates; without it one CTA
+ * takes a whole row.  The results are the same.
  * Replaces tallax/_src/top_k.py:482-506 (top_dynamic_k) and
  * tallax/_src/bitonic_top_k.py:390-401 (bitonic_top_k).                             */
 #define TLX_TOPK_MAX_K 2048
