@@ -1949,7 +1949,7 @@ static size_t counters_bytes(int64_t rows) { return 256 + (((size_t)rows * sizeo
 // ---- streaming path (sampler_stream.cuh): workspace layout and launches ---------------------------
 struct StreamLayout {
   int P, part_chunks, nchunks, nfin;
-  size_t off_desc, off_counts, off_lump, off_flag, off_state, off_records, off_hist, off_cands, off_timeline = 0, bytes;
+  size_t off_desc, off_counts, off_lump, off_flag, off_rowdone, off_state, off_records, off_hist, off_cands, off_timeline = 0, bytes;
 };
 static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 static StreamLayout stream_layout(int64_t rows, int64_t vocab) {
@@ -1964,6 +1964,7 @@ static StreamLayout stream_layout(int64_t rows, int64_t vocab) {
   l.off_counts = o;  o = align256(o + (size_t)rows * l.P * kStWarps * sizeof(int));
   l.off_lump = o;    o = align256(o + (size_t)rows * l.P * sizeof(double));
   l.off_flag = o;    o = align256(o + (size_t)rows * sizeof(int));
+  l.off_rowdone = o; o = align256(o + (size_t)rows * sizeof(int));
   l.off_state = o;   o = align256(o + (size_t)rows * sizeof(WideState));
   l.off_records = o; o = align256(o + (size_t)rows * l.nfin * sizeof(FinRecord));
   l.off_hist = o;    o = align256(o + (size_t)rows * kStWin * sizeof(uint32_t));
@@ -2072,10 +2073,12 @@ static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* wor
   p.fin_ctas = final_in_stream ? 0 : (3 * sms - (int)sp.rows < sms ? sms : 3 * sms - (int)sp.rows);
   p.error_flag = (int*)ws;
   p.item_counter = (int*)ws + 1;
+  p.row_signals = (int*)ws + 2;
   p.desc = (StreamDesc*)(ws + l.off_desc);
   p.counts = (int*)(ws + l.off_counts);
   p.wlump = (double*)(ws + l.off_lump);
   p.wflag = (int*)(ws + l.off_flag);
+  p.rowdone = (int*)(ws + l.off_rowdone);
   p.wstate = (WideState*)(ws + l.off_state);
   p.records = (FinRecord*)(ws + l.off_records);
   p.whist = (uint32_t*)(ws + l.off_hist);

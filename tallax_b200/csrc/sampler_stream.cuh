@@ -120,6 +120,9 @@ struct StreamParams {
   FinRecord* records;    // [rows * nfin]
   int fin_items;             // final items per wide row (kStFinalElems elements each); 0: the finish
                              // kernel makes the final pass over the wide rows
+  int* rowdone;              // per row: parts of a normal row whose candidate lists are complete
+  int* row_signals;          // 1 once the stream kernel has decided to count them (it does when the batch has
+                             // wide rows, whose final items keep it busy long after the normal rows are done)
   int* item_counter;     // [1] next unclaimed item - gridDim.x (cleared by the prologue)
   int* error_flag;       // [1] a bounded wait of the stream kernel gave up (cleared by the prologue)
   int debug;             // diagnostic switches, 0 in normal use
@@ -379,8 +382,9 @@ __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamPa
     StreamDesc d;
     d.cls = cls; d.K = K; d.key16 = key16; d.xref = xref;
     p.desc[row] = d;
+    p.rowdone[row] = 0;
     if (p.sp.out_status) p.sp.out_status[row] = 0;
-    if (row == 0) { *p.error_flag = 0; *p.item_counter = 0; }
+    if (row == 0) { *p.error_flag = 0; *p.item_counter = 0; *p.row_signals = 0; }
   }
   TLX_STAMP(p.sp, 1);
 }
@@ -620,7 +624,6 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   const int lane = lane_id(), warp = warp_id();
   const int first_rows = (int)(gridDim.x / (unsigned)p.P);
   TLX_STAMP(p.sp, 0);
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the finish kernel's CTAs move in as these leave
   // the first item's copies need nothing but the CTA's index
   StProducer ps;
   ps.item = 0;
@@ -674,6 +677,10 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   }
   // everything below reads what the prologue kernel wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The finish kernel's CTAs move in as these leave.  Released only here, after the wait: a finish CTA then
+  // starts after the prologue kernel has completed, and may read the rows' descriptors and completion
+  // counters without waiting for this whole kernel.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   TLX_STAMP(p.sp, 6);
   if (threadIdx.x == 0) ps.next = atomicAdd(p.item_counter, 1);
   for (int r = threadIdx.x; r < rows; r += kStThreads) {
@@ -689,6 +696,10 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   order.nwide_items = (nwide - nwide_first) * p.P;
   order.nnormal_items = (nlisted - nwide) * p.P;
   order.nfinal_items = nwide * p.fin_items;
+  // Counting the rows' finished parts costs the producer thread a fence per item: worth it only when final
+  // items will keep this kernel busy after the normal rows are complete.
+  const bool signal_rows = order.nfinal_items > 0;
+  if (signal_rows && blockIdx.x == 0 && threadIdx.x == 0) *reinterpret_cast<volatile int*>(p.row_signals) = 1;
   if (threadIdx.x == 0) {
     // a first item shorter than the ring: go on into the claimed items
     for (int s = ps.chunk; s < kStSlots; ++s) st_issue(p, ps, order, ring, ctl, s);
@@ -783,6 +794,10 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         }
       }
       __syncthreads();   // the producer's fifo entries are visible; ctl is free again
+      if (threadIdx.x == 0) {   // the item's record (if any) is in: the row's finish CTA counts the items
+        __threadfence();
+        atomicAdd(&p.wstate[row].done, 1);
+      }
       if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + 3;
       continue;
     }
@@ -868,6 +883,12 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
       }
     }
     __syncthreads();   // the producer's fifo entries are visible; the shared window is free again
+    if (signal_rows && cls == kStNormal && threadIdx.x == 0) {
+      // this part's candidates and counts are written (all warps, before the barrier): the fence makes them
+      // visible before the count that the row's finish CTA waits for
+      __threadfence();
+      atomicAdd(&p.rowdone[row], 1);
+    }
     if (taken == 1) TLX_STAMP(p.sp, 3);
     if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + cls;
   }
@@ -1548,9 +1569,29 @@ static __device__ __forceinline__ void st_finish_row(const StreamParams& p, int 
   TailShared& t = *reinterpret_cast<TailShared*>(smem);
   const SampleParams& sp = p.sp;
   for (int i = threadIdx.x; i < kTlBins; i += kStThreads) t.hist[i] = 0;
-  asm volatile("griddepcontrol.wait;" ::: "memory");   // the stream kernel's lists and thresholds are complete
+  // This CTA started after the prologue kernel had completed (see the stream kernel): the row's descriptor is
+  // there.  It waits for its own row only: a normal row's P parts, a wide row's final items; the stream kernel
+  // may go on with other rows meanwhile.  The waits are bounded; past the bound (and for rows that the
+  // whole-row routines take) the CTA waits for the whole stream kernel.
+  static_assert(sizeof(StreamDesc) == 16, "StreamDesc is read as one 16-byte word");
+  const uint4 draw = __ldcg(reinterpret_cast<const uint4*>(p.desc + row));
+  StreamDesc d;
+  memcpy(&d, &draw, sizeof(d));
+  if (threadIdx.x == 0) {
+    volatile const int* flag = nullptr;
+    int want = 0;
+    const bool signals = *reinterpret_cast<volatile const int*>(p.row_signals) != 0;
+    if (d.cls == kStNormal && signals) { flag = p.rowdone + row; want = p.P; }
+    else if (d.cls == kStWide && p.fin_items > 0) { flag = &p.wstate[row].done; want = p.fin_items; }
+    bool ready = false;
+    if (flag && !(p.debug & 16)) {
+      for (int spin = 0; spin < (1 << 18) && !(ready = *flag >= want); ++spin) __nanosleep(100);
+    }
+    if (!ready) asm volatile("griddepcontrol.wait;" ::: "memory");
+    __threadfence();
+  }
+  __syncthreads();
   // one round trip for everything the row's short path reads first (whatever the row's class turns out to be)
-  const StreamDesc d = p.desc[row];
   const float pp = sp.top_p[row], T_ = sp.temperature[row];
   const int timeout = __ldcg(p.error_flag) ? (int)kStatusTimeout : 0;
   const TailFetch fetched = tl_fetch(p, row);
@@ -1579,6 +1620,9 @@ static __device__ __forceinline__ void st_finish_row(const StreamParams& p, int 
   TLX_STAMP(sp, 8);
   if (threadIdx.x == 0 && sp.timeline) sp.timeline[(size_t)blockIdx.x * 16 + 9] = d.cls;
   if (slow) st_slow_row(p, row, smem);
+  // this kernel must not be complete before the stream kernel is: whatever follows on the stream may reuse
+  // the workspace
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 constexpr size_t kStFinishRowSmem =
