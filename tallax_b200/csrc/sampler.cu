@@ -2115,8 +2115,7 @@ static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* wor
   sample_prologue_kernel<<<(unsigned)sp.rows, kStProThreads, 0, st>>>(p);
   TLX_CHECK_LAUNCH("sample (prologue)");
   if (stages < 2) return TLX_OK;
-  int64_t sgrid = items < 4ll * sms ? items : 4ll * sms;
-  sgrid -= sgrid % l.P;   // whole rows in the first wave (see sample_stream_kernel)
+  const int64_t sgrid = items < 4ll * sms ? items : 4ll * sms;
   TLX_TIMELINE_KERNEL(1);
   if ((rc = launch_dependent(sample_stream_kernel, (unsigned)sgrid, kStThreads, st_smem, st, "sample (stream)", p)) != TLX_OK) return rc;
   if (stages < 3) return TLX_OK;

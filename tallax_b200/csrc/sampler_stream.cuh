@@ -471,11 +471,10 @@ __device__ __forceinline__ void st_hist_chunk(const unsigned char* buf, int nvec
 
 // The producer's state (thread 0): the item whose chunks are being requested, and the one claimed for
 // afterwards (its value is first used an item later, so the counter's round trip stays off the path).
-// Items: the first gridDim.x of them (one per CTA, no claim needed) are the parts of the first
-// gridDim.x / P rows in their natural order, so that their copies can be requested before anything about
-// the rows is known.  The items claimed from the counter are the parts of the remaining rows: those of the
-// wide rows (they take longest) early, but only every third item, so that an SM rarely works on several
-// of them at a time; rows of class "other" are not streamed.
+// The list of items is built from the rows' parameters (no need to wait for the prologue kernel): a CTA's
+// first item is the one of its own index, so its copies are requested before anything about the rows'
+// contents is known; further items are claimed from a counter.  Rows of class "other" are not streamed.
+constexpr int kStClaimLate = -2;   // StProducer::next: no item claimed ahead, claim when one is needed
 struct StProducer {
   int item;    // >= 0: there is an item (its code); -1: no more
   int row, part, chunk, nchunks;
@@ -486,31 +485,26 @@ struct StProducer {
 // Item codes: row << 8 | part for the logits of a part of a row; row << 8 | 0x80 | sub for a final item
 // (logits and noise of the elements [sub * kStFinalElems, (sub + 1) * kStFinalElems) of a wide row).
 struct StOrder {
-  const unsigned short* rows;   // all wide rows, then the normal rows behind the first wave
-  int nwide_all, nwide_first;   // wide rows; those of them inside the first wave (the list's first entries)
+  const unsigned short* rows;   // the wide rows, then the normal rows (each in row order)
+  int nwide;
   int nwide_items, nnormal_items, nfinal_items;
-  // claimed index -> code, or -1 past the end
+  // item index -> code, or -1 past the end.  Order: the wide rows' histogram items (every CTA's first item
+  // is taken by its index, so these start at once, at most one per CTA while there are CTAs enough: the rows'
+  // thresholds are what the final items wait for), the normal rows' items, the final items.
   __device__ __forceinline__ int item(int j, int P, int fin_items) const {
-    if (j >= nwide_items + nnormal_items) {
-      j -= nwide_items + nnormal_items;
-      if (j >= nfinal_items) return -1;
-      const int w = j / fin_items;
-      return ((int)rows[w] << 8) | 0x80 | (j - w * fin_items);
+    if (j < nwide_items) {
+      const int r = j / P;
+      return ((int)rows[r] << 8) | (j - r * P);
     }
-    int idx;   // index into the wide items (< nwide_items) or nwide_items + index into the normal items
-    if (nnormal_items >= 2 * nwide_items) {
-      if (j < 3 * nwide_items) idx = j % 3 == 0 ? j / 3 : nwide_items + (j - j / 3 - 1);
-      else idx = j;
-    } else {
-      idx = j;   // too few normal items to spread the wide ones: wide first
+    j -= nwide_items;
+    if (j < nnormal_items) {
+      const int r = j / P;
+      return ((int)rows[nwide + r] << 8) | (j - r * P);
     }
-    if (idx < nwide_items) {
-      const int r = idx / P;
-      return ((int)rows[nwide_first + r] << 8) | (idx - r * P);
-    }
-    idx -= nwide_items;
-    const int r = idx / P;
-    return ((int)rows[nwide_all + r] << 8) | (idx - r * P);
+    j -= nnormal_items;
+    if (j >= nfinal_items) return -1;
+    const int w = j / fin_items;
+    return ((int)rows[w] << 8) | 0x80 | (j - w * fin_items);
   }
 };
 
@@ -561,6 +555,7 @@ __device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, 
   for (;;) {
     if (ps.item < 0) return;
     if (ps.chunk < ps.nchunks) break;
+    if (ps.next == kStClaimLate) ps.next = (int)gridDim.x + atomicAdd(p.item_counter, 1);
     const int code = order.item(ps.next, p.P, p.fin_items);
     ps.item = code;
     if (code >= 0) {
@@ -568,7 +563,10 @@ __device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, 
       ps.part = code & 0xFF;
       ps.chunk = 0;
       ps.nchunks = st_code_chunks(p, code);
-      ps.next = atomicAdd(p.item_counter, 1);
+      // The next item is claimed now, an item ahead, so that the counter's round trip stays off the path --
+      // except behind a final item: those are the last items of the list and long ones, and a CTA that
+      // holds one must not sit on a second one while other CTAs run out of work.
+      ps.next = (code & 0x80) ? kStClaimLate : (int)gridDim.x + atomicAdd(p.item_counter, 1);
     }
     ctl.fifo[ps.pushed & 7] = code;
     ps.pushed++;
@@ -622,51 +620,35 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   unsigned short* order_rows = reinterpret_cast<unsigned short*>(dtab + p.sp.rows);
   const int rows = (int)p.sp.rows;
   const int lane = lane_id(), warp = warp_id();
-  const int first_rows = (int)(gridDim.x / (unsigned)p.P);
   TLX_STAMP(p.sp, 0);
-  // the first item's copies need nothing but the CTA's index
-  StProducer ps;
-  ps.item = 0;
-  ps.row = (int)(blockIdx.x / (unsigned)p.P);
-  ps.part = (int)(blockIdx.x % (unsigned)p.P);
-  ps.chunk = 0;
-  ps.nchunks = st_part_chunks(p, ps.part);
-  ps.next = 0;
-  ps.pushed = 1;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStSlots; ++s) mbar_init(&ctl.mbar[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    ctl.fifo[0] = (ps.row << 8) | ps.part;
-    for (int s = 0; s < kStSlots && s < ps.nchunks; ++s) st_issue_chunk(p, ps, ring, ctl, s);
   }
-  // The list of rows behind the first wave needs the rows' classes only as far as the parameters decide
-  // them (a row that the prologue downgrades is dropped when its items come up): it is built while the
-  // prologue kernel still runs.  All wide rows in row order (those of the first wave come first), then
-  // the normal rows behind the first wave.
+  // The list of rows needs the rows' classes only as far as the parameters decide them (a row that the
+  // prologue downgrades is dropped when its items come up): it is built while the prologue kernel still runs.
   uint32_t* pcls = dtab;   // parameter classes, replaced by the descriptors below
   for (int r = threadIdx.x; r < rows; r += kStThreads) {
     int K;
     pcls[r] = (uint32_t)st_param_class(p.sp.top_k[r], p.sp.top_p[r], p.sp.temperature[r], p.sp.vocab, K);
   }
   __syncthreads();
-  int nlisted = 0, nwide = 0, nwide_first = 0;
+  int nlisted = 0, nwide = 0;
 #pragma unroll 1
   for (int pass = 0; pass < 2; ++pass) {
     const uint32_t want = pass == 0 ? (uint32_t)kStWide : (uint32_t)kStNormal;
 #pragma unroll 1
-    for (int base = pass == 0 ? 0 : first_rows; base < rows; base += kStThreads) {
+    for (int base = 0; base < rows; base += kStThreads) {
       const int r = base + (int)threadIdx.x;
       const bool take = r < rows && pcls[r] == want;
       const uint32_t mask = __ballot_sync(0xFFFFFFFFu, take);
-      const uint32_t early = __ballot_sync(0xFFFFFFFFu, take && r < first_rows);
-      if (lane == 0) { ctl.ibest[warp] = __popc(mask); ctl.wtok[warp] = __popc(early); }
+      if (lane == 0) ctl.ibest[warp] = __popc(mask);
       __syncthreads();
       int off = nlisted, total = 0;
 #pragma unroll 1
       for (int w = 0; w < kStWarps; ++w) {
         if (w < warp) off += ctl.ibest[w];
         total += ctl.ibest[w];
-        if (pass == 0) nwide_first += ctl.wtok[w];
       }
       if (take && TLX_IN_BOUNDS(off + __popc(mask & ((1u << lane) - 1u)), rows, 10))
         order_rows[off + __popc(mask & ((1u << lane) - 1u))] = (unsigned short)r;
@@ -675,6 +657,25 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
     }
     if (pass == 0) nwide = nlisted;
   }
+  StOrder order;
+  order.rows = order_rows;
+  order.nwide = nwide;
+  order.nwide_items = nwide * p.P;
+  order.nnormal_items = (nlisted - nwide) * p.P;
+  order.nfinal_items = nwide * p.fin_items;
+  // the CTA's first item, and its first copies
+  StProducer ps;
+  ps.item = order.item((int)blockIdx.x, p.P, p.fin_items);
+  ps.row = ps.item >> 8;
+  ps.part = ps.item & 0xFF;
+  ps.chunk = 0;
+  ps.nchunks = ps.item >= 0 ? st_code_chunks(p, ps.item) : 0;
+  ps.next = 0;
+  ps.pushed = 1;
+  if (threadIdx.x == 0) {
+    ctl.fifo[0] = ps.item;
+    for (int s = 0; s < kStSlots && s < ps.nchunks; ++s) st_issue_chunk(p, ps, ring, ctl, s);
+  }
   // everything below reads what the prologue kernel wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // The finish kernel's CTAs move in as these leave.  Released only here, after the wait: a finish CTA then
@@ -682,20 +683,13 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   // counters without waiting for this whole kernel.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   TLX_STAMP(p.sp, 6);
-  if (threadIdx.x == 0) ps.next = atomicAdd(p.item_counter, 1);
+  if (threadIdx.x == 0) ps.next = (int)gridDim.x + atomicAdd(p.item_counter, 1);
   for (int r = threadIdx.x; r < rows; r += kStThreads) {
     const StreamDesc d = p.desc[r];
     dtab[r] = ((uint32_t)d.cls << 16) | (uint32_t)d.key16;
   }
   __syncthreads();
   TLX_STAMP(p.sp, 7);
-  StOrder order;
-  order.rows = order_rows;
-  order.nwide_all = nwide;
-  order.nwide_first = nwide_first;
-  order.nwide_items = (nwide - nwide_first) * p.P;
-  order.nnormal_items = (nlisted - nwide) * p.P;
-  order.nfinal_items = nwide * p.fin_items;
   // Counting the rows' finished parts costs the producer thread a fence per item: worth it only when final
   // items will keep this kernel busy after the normal rows are complete.
   const bool signal_rows = order.nfinal_items > 0;
@@ -720,6 +714,10 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         // the row's threshold: settled by whoever brought the last part of its histogram.  Those items were
         // all claimed before this one, by CTAs that wait for nothing but their copies, so the wait is
         // short; it is bounded all the same.
+#ifdef TLX_TIMELINE
+        const long long tl_f0 = global_timer_ns();
+        if (p.sp.timeline && p.sp.timeline[(size_t)blockIdx.x * 16 + 13] == 0) p.sp.timeline[(size_t)blockIdx.x * 16 + 13] = tl_f0;
+#endif
         volatile int* rp = &p.wstate[row].result;
         const float T_ = p.sp.temperature[row];                                             // one round trip
         const uint32_t bk = *reinterpret_cast<volatile uint32_t*>(&p.wstate[row].best_key);  // for all three
@@ -732,6 +730,9 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         ctl.fin_result = res;
         ctl.best_key = bk;
         ctl.fin_T = T_;
+#ifdef TLX_TIMELINE
+        if (p.sp.timeline) { p.sp.timeline[(size_t)blockIdx.x * 16 + 12] += 1; p.sp.timeline[(size_t)blockIdx.x * 16 + 14] += global_timer_ns() - tl_f0; }
+#endif
       }
       __syncthreads();
       const int res = ctl.fin_result;
