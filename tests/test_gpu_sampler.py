@@ -290,3 +290,27 @@ def test_shard_candidates_of_many_short_rows(cuda, dtype, v_local, k):
     gv, gi, gn = to_np(got[0]), to_np(got[1].view(torch.int32)), to_np(got[2])
     assert np.array_equal(gi, ei)
     assert np.array_equal(gv, ev, equal_nan=True) and np.array_equal(gn, en)
+
+
+@pytest.mark.parametrize("B", [1, 2, 5, 600, 2048])
+def test_streaming_path_row_counts(cuda, B):
+    # fewer items than CTAs, more rows than finish CTAs resident at a time, and rows of every class in one batch;
+    # the oracle checks a sample of the rows, repeat calls check determinism of the rest
+    V = 32768
+    x, tk, tp, T, noise = o.make_sampling_inputs(B=B, V=V, seed=50 + B, dtype="bf16")
+    tk[::7] = 0
+    if B > 3:
+        tp[3] = 1.0
+        tk[3] = 0       # no filter at all: the whole-row routine
+        T[4] = 0.0      # greedy
+    args = [to_dev(a, cuda) for a in (x, tk, tp, T)]
+    dn = to_dev(noise, cuda)
+    tok, status = ops.sample(*args, noise=dn, return_status=True)
+    got = to_np(tok).copy()
+    assert (to_np(status) & 2 == 0).all()
+    sel = np.unique(np.concatenate([np.arange(min(B, 8)), np.random.default_rng(B).integers(0, B, 40)]))
+    exp, flags = o.sample(x[sel], tk[sel], tp[sel], T[sel], noise=noise[sel], return_flags=True)
+    assert not ((got[sel] != exp) & ~flags).any()
+    for _ in range(2):
+        again, _ = ops.sample(*args, noise=dn, return_status=True)
+        assert np.array_equal(to_np(again), got)
