@@ -150,6 +150,13 @@ int tlx_top_k(void* stream, const void* x, int dtype, int64_t rows, int64_t n, i
               void* out_vals, int32_t* out_idx, int32_t* out_valid, int32_t* out_depths,
               void* out_cutoff, void* workspace, size_t workspace_bytes);
 
+/* ---- canonical keys ---------------------------------------------------------------
+ * In place: every float of x[count] becomes what it is after the round trip through the
+ * order-preserving key (-0 -> +0, every NaN -> the canonical NaN); integers are left alone.
+ * The sort's first key leaves tlx_sort in this form; this is for the further keys of a
+ * multi-key sort, which are gathered through the final permutation (tallax/_src/sort.py:834-839). */
+int tlx_canonicalize_keys(void* stream, void* x, int dtype, int64_t count);
+
 /* ---- counter-based noise -------------------------------------------------------
  * out[i] = max(minval, f * (maxval - minval) + minval), f the [0,1) float made from
  * x0^x1 of threefry2x32(key, (0, idx0[i]*dim1_size + idx1[i])).

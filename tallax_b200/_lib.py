@@ -34,6 +34,7 @@ SIGNATURES = {
     "tlx_top_k_workspace_bytes": (_sz, [_i64, _i64, _i32]),
     "tlx_top_k": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i32, _vp, _i32, _f64, _i32, _vp, _vp, _vp, _vp, _vp,
                          _vp, _sz]),
+    "tlx_canonicalize_keys": (_i32, [_vp, _vp, _i32, _i64]),
     "tlx_sparse_random_uniform": (_i32, [_vp, _u32, _u32, _vp, _vp, _i64, _i64, _f32, _f32, _vp]),
     "tlx_sparse_random_uniform_dev": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _f32, _vp]),
     "tlx_gumbel_argmax_dev": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i32, _vp]),

@@ -126,6 +126,16 @@ def cumsum(arr: torch.Tensor, axis: int, reverse: bool = False) -> torch.Tensor:
     return out
 
 
+def canonicalize_keys_(x: torch.Tensor) -> torch.Tensor:
+    """In place: floats as they look after the key-domain round trip (-0 -> +0, canonical NaN)."""
+    x = _dev(x)
+    if x.is_floating_point():
+        if not x.is_contiguous():
+            raise ValueError("canonicalize_keys_ needs a contiguous tensor")
+        check(_lib.load().tlx_canonicalize_keys(_stream(), _ptr(x), dtype_code(x), x.numel()))
+    return x
+
+
 def argmax(keys: torch.Tensor, axis: int) -> torch.Tensor:
     keys = _dev(keys)
     out = torch.empty(keys.shape[1 - axis], dtype=torch.int32, device=keys.device)

@@ -18,8 +18,9 @@ def canonicalize_operand(operand):
 
 
 def _canonical_float(x):
-    # what a key looks like after the key-domain round trip: -0 -> +0
-    return x + 0 if x.is_floating_point() else x
+    # what a key looks like after the key-domain round trip (-0 -> +0, canonical NaN): in place, by the
+    # library's own kernel (x is the freshly gathered output)
+    return ops.canonicalize_keys_(x)
 
 
 def sort(operand, num_keys: int, is_stable: bool = False, return_argsort: bool = False, descending: bool = False,

@@ -224,6 +224,16 @@ __global__ void sparse_uniform_kernel(uint32_t k0, uint32_t k1, const uint32_t* 
   }
 }
 
+// ---------------------------------------------------------------------------------
+// key outputs in canonical form: what a float looks like after the round trip through the
+// order-preserving key (-0 -> +0, every NaN -> the one canonical NaN), in place
+// ---------------------------------------------------------------------------------
+template <int DT>
+__global__ void canonicalize_kernel(typename Elem<DT>::type* __restrict__ x, int64_t count) {
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < count; e += (int64_t)gridDim.x * blockDim.x)
+    x[e] = Elem<DT>::from_key(Elem<DT>::key(x[e]));
+}
+
 }  // namespace tlx
 
 using namespace tlx;
@@ -308,6 +318,23 @@ static int sparse_random_uniform_impl(void* stream, uint32_t key0, uint32_t key1
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   sparse_uniform_kernel<<<blocks, 256, 0, st>>>(key0, key1, key_dev, idx0, idx1, count, dim1_size, minval, maxval, out);
   TLX_CHECK_LAUNCH("sparse_random_uniform");
+  return TLX_OK;
+}
+
+int tlx_canonicalize_keys(void* stream, void* x, int dtype, int64_t count) {
+  cudaStream_t st = (cudaStream_t)stream;
+  TLX_CHECK_ARG(count >= 0, "canonicalize_keys: negative extent");
+  if (count == 0 || dtype == TLX_I32 || dtype == TLX_U32) return TLX_OK;   // integers are their own canonical form
+  TLX_CHECK_ARG(x, "canonicalize_keys: null pointer");
+  const int64_t want = (count + 255) / 256;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  switch (dtype) {
+    case TLX_F32: canonicalize_kernel<TLX_F32><<<blocks, 256, 0, st>>>((float*)x, count); break;
+    case TLX_BF16: canonicalize_kernel<TLX_BF16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)x, count); break;
+    case TLX_F16: canonicalize_kernel<TLX_F16><<<blocks, 256, 0, st>>>((__half*)x, count); break;
+    default: return set_error(TLX_ERR_UNSUPPORTED, "canonicalize_keys: dtype %d not supported", dtype);
+  }
+  TLX_CHECK_LAUNCH("canonicalize_keys");
   return TLX_OK;
 }
 
