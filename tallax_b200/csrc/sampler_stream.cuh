@@ -564,9 +564,11 @@ __device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, 
       ps.chunk = 0;
       ps.nchunks = st_code_chunks(p, code);
       // The next item is claimed now, an item ahead, so that the counter's round trip stays off the path --
-      // except behind a final item: those are the last items of the list and long ones, and a CTA that
-      // holds one must not sit on a second one while other CTAs run out of work.
-      ps.next = (code & 0x80) ? kStClaimLate : (int)gridDim.x + atomicAdd(p.item_counter, 1);
+      // except behind a final item when there are fewer final items than CTAs: those are the last items of
+      // the list and long ones, and a CTA that holds one must not sit on a second one while other CTAs run
+      // out of work.  (With many final items per CTA claiming late would leave the ring dry at every item.)
+      ps.next = ((code & 0x80) && order.nfinal_items <= (int)gridDim.x) ? kStClaimLate
+                                                                        : (int)gridDim.x + atomicAdd(p.item_counter, 1);
     }
     ctl.fifo[ps.pushed & 7] = code;
     ps.pushed++;
