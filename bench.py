@@ -40,6 +40,13 @@ WORKLOAD = ("fused temperature/top-k/top-p/noise sampling, bf16 logits [256,1282
             "uniform noise [256,128256]")
 
 
+def bench_config(rows_call, world):
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": WORKLOAD, "batch_per_gpu": rows_call, "vocab": V, "sharding": f"batch rows x{world}",
+            "l2": f"{N_SETS} rotating input sets ({N_SETS * rows_call * V * 6 / 1e6:.0f} MB of logits and noise > 126 MB "
+                  "L2)"}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -175,7 +182,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch_per_step": rows, "vocab": V},
+        "config": bench_config(B, int(os.environ.get("WORLD_SIZE", "1"))),   # the GPU arm's config, key for key
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": len(chunks), "kind": "port",
                          "sample": f"{'all' if rows == B else 'the first'} {rows} of the 256 rows of input set 0 per "
                                    "step, NumPy restatement (JAX is not installable here)"},
@@ -392,9 +399,7 @@ def run_ours(args):
             "metric": METRIC, "value": world * rows_call * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_gpu": rows_call, "vocab": V, "sharding": f"batch rows x{world}",
-                       "l2": f"{N_SETS} rotating input sets ({N_SETS * rows_call * V * 6 / 1e6:.0f} MB of logits and "
-                             "noise > 126 MB L2)"},
+            "config": bench_config(rows_call, world),
             "clocks": clocks.summary(),
             "ms_per_step_by_rank": [t / args.steps for t in per_rank],
             "launch": "one CUDA graph launch per step" if graphs else "one library call per step",
