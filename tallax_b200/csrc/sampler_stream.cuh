@@ -154,6 +154,12 @@ __device__ __forceinline__ bool mbar_wait_suspended(unsigned long long* bar, uin
   }
   return false;
 }
+// Adds to a counter in global memory with release semantics at GPU scope: every write that this thread has
+// made or has observed through a CTA barrier is visible to a thread that then reads the new count.  One
+// instruction; the thread does not wait for the writes itself (a fence followed by a relaxed add would).
+__device__ __forceinline__ void red_release_add(int* ptr, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void prefetch_l2(const void* ptr) { asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr)); }
 
 // Scratch of wide_threshold_core (up to 16 warps).
@@ -797,10 +803,8 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         }
       }
       __syncthreads();   // the producer's fifo entries are visible; ctl is free again
-      if (threadIdx.x == 0) {   // the item's record (if any) is in: the row's finish CTA counts the items
-        __threadfence();
-        atomicAdd(&p.wstate[row].done, 1);
-      }
+      // the item's record (if any) is in: the row's finish CTA counts the items
+      if (threadIdx.x == 0) red_release_add(&p.wstate[row].done, 1);
       if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + 3;
       continue;
     }
@@ -887,10 +891,9 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
     }
     __syncthreads();   // the producer's fifo entries are visible; the shared window is free again
     if (signal_rows && cls == kStNormal && threadIdx.x == 0) {
-      // this part's candidates and counts are written (all warps, before the barrier): the fence makes them
-      // visible before the count that the row's finish CTA waits for
-      __threadfence();
-      atomicAdd(&p.rowdone[row], 1);
+      // this part's candidates and counts are written (all warps, before the barrier): the release makes
+      // them visible before the count that the row's finish CTA waits for
+      red_release_add(&p.rowdone[row], 1);
     }
     if (taken == 1) TLX_STAMP(p.sp, 3);
     if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + cls;
