@@ -180,6 +180,7 @@ struct __align__(16) StControl {
   int flag;
   int vstar;
   uint32_t best_key;      // final pass: the CTA's best screened score so far, as an ordered key
+  int pending[8];         // stream: rows of the normal items finished but not yet counted in rowdone (thread 0)
   int fin_result;         // final item: the row's WideState::result
   float fin_T;            // ... and temperature
   double dsum[kStWarps];
@@ -615,6 +616,15 @@ __device__ __forceinline__ void st_final_chunk(const unsigned char* buf, int ngr
   }
 }
 
+// Counts the noted items in their rows' rowdone (thread 0): one fence for all of them, then plain adds.
+__device__ __forceinline__ int st_publish_rows(const StreamParams& p, StControl& ctl, int n) {
+  if (n > 0) {
+    __threadfence();
+    for (int i = 0; i < n; ++i) atomicAdd(&p.rowdone[ctl.pending[i]], 1);
+  }
+  return 0;
+}
+
 // Shared memory beyond the fixed part: per row 4 bytes of descriptor (class << 16 | key) and 2 bytes of order.
 // The grid is a multiple of P (whole rows in the first wave) and at most rows * P.
 __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamParams p) {
@@ -712,6 +722,7 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
   int slot = 0;
   uint32_t phase = 0;
   int taken = 0;   // items this CTA has started
+  int npending = 0;   // thread 0: entries of ctl.pending
   TLX_STAMP(p.sp, 1);
   for (int code = ctl.fifo[0]; code >= 0; code = ctl.fifo[taken & 7]) {
     ++taken;
@@ -719,6 +730,7 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
     if (code & 0x80) {
       // ---- a final item: the Gumbel arg-max over the kept elements of a range of a wide row
       if (threadIdx.x == 0) {
+        npending = st_publish_rows(p, ctl, npending);
         // the row's threshold: settled by whoever brought the last part of its histogram.  Those items were
         // all claimed before this one, by CTAs that wait for nothing but their copies, so the wait is
         // short; it is bounded all the same.
@@ -891,13 +903,17 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
     }
     __syncthreads();   // the producer's fifo entries are visible; the shared window is free again
     if (signal_rows && cls == kStNormal && threadIdx.x == 0) {
-      // this part's candidates and counts are written (all warps, before the barrier): the release makes
-      // them visible before the count that the row's finish CTA waits for
-      red_release_add(&p.rowdone[row], 1);
+      // This part's candidates and counts are written (all warps, before the barrier).  The row's finish CTA
+      // waits for the count of finished parts; publishing it needs a release, which holds this thread (the
+      // producer) up for a round trip, so finished items are noted and published together: when the list is
+      // full, before a final item, at the end.  Finish CTAs find room only when CTAs of this kernel leave.
+      ctl.pending[npending++] = row;
+      if (npending == 8) npending = st_publish_rows(p, ctl, npending);
     }
     if (taken == 1) TLX_STAMP(p.sp, 3);
     if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + cls;
   }
+  if (threadIdx.x == 0) st_publish_rows(p, ctl, npending);
   TLX_STAMP(p.sp, 4);
 }
 
