@@ -787,6 +787,9 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         if (threadIdx.x == 0) st_issue(p, ps, order, ring, ctl, slot);
         if (++slot == kStSlots) { slot = 0; phase ^= 1u; }
       }
+#ifdef TLX_TIMELINE
+      if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 15] = global_timer_ns() - p.sp.timeline[(size_t)blockIdx.x * 16 + 13];
+#endif
       if (res >= 0) {
         // the item's record: its best element, and whether anything else of it comes within the slack
         const uint32_t key = f32_key(a1);
@@ -817,6 +820,9 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
       __syncthreads();   // the producer's fifo entries are visible; ctl is free again
       // the item's record (if any) is in: the row's finish CTA counts the items
       if (threadIdx.x == 0) red_release_add(&p.wstate[row].done, 1);
+#ifdef TLX_TIMELINE
+      if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 9] = global_timer_ns() - p.sp.timeline[(size_t)blockIdx.x * 16 + 13];
+#endif
       if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 5] = taken * 16 + 3;
       continue;
     }
