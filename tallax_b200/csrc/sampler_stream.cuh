@@ -585,17 +585,23 @@ __device__ __forceinline__ void st_issue(const StreamParams& p, StProducer& ps, 
 
 // A chunk of a final item: logits (front of the slot) and noise (behind them) of the elements [elem0,
 // elem0 + 8 ngroups) of a wide row; a thread takes one group of eight.  Kept elements (value not below
-// tvf) whose noise passes the test 1 - u <= eps (see the main loop) are scored.
+// tvf) whose noise passes the test below are scored.
+// The test: with cbm = (a score that some kept element of the row reaches) - margin, an element of value x
+// and noise u can come within the screening slack of the row's best score only if x / T + g(u) >= cbm,
+// g = -log(-log u); since -log u >= 1 - u that needs 1 - u <= exp(-(cbm - x / T)).  It is made once per
+// group with the group's greatest value, which only loosens it.
 // Per thread: the best two screened scores of the item so far (a1 >= a2), with the best one's noise, bf16
 // bits and token.
 __device__ __forceinline__ void st_final_chunk(const unsigned char* buf, int ngroups, int elem0, __nv_bfloat162 tv2,
-                                               float tvf, float inv_T, float eps, float& a1, float& a2, float& u1,
+                                               float tvf, float inv_T, float cbm, float& a1, float& a2, float& u1,
                                                uint32_t& b1, int& t1) {
   const int v = (int)threadIdx.x;
   if (v >= ngroups) return;
   const uint4 x = *reinterpret_cast<const uint4*>(buf + (size_t)v * 16);
   const __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(bf162_bits(x.x), bf162_bits(x.y)), __hmax2_nan(bf162_bits(x.z), bf162_bits(x.w)));
   if (__hblt2(m, tv2)) return;   // all eight below the threshold
+  const float xg = fmaxf(__low2float(m), __high2float(m));   // NaN-propagating max: a NaN keeps the test open
+  const float eps = xg == xg ? __expf(-(cbm - xg * inv_T)) * 1.00001f : INFINITY;
   const float* nbuf = reinterpret_cast<const float*>(buf + kStFinalChunkElems * 2) + v * 8;
   const float4 n0 = *reinterpret_cast<const float4*>(nbuf);
   const float4 n1 = *reinterpret_cast<const float4*>(nbuf + 4);
@@ -760,24 +766,21 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
       const uint32_t tbits = key16_bf16_bits((uint32_t)wide_vstar16(res));
       const __nv_bfloat162 tv2 = bf162_splat_bits(tbits);
       const float tvf = __uint_as_float(tbits << 16);
-      const float xtop = key16_value(wide_kmax16(res)) * inv_T;
       const int nc = st_final_item_chunks(p, part);
       const int64_t last_elems = p.sp.vocab - ((int64_t)part * kStFinalElems + (int64_t)(nc - 1) * kStFinalChunkElems);
       float a1 = -INFINITY, a2 = -INFINITY, u1 = 0.5f, published = -INFINITY;
       uint32_t b1 = 0;
       int t1 = 0x7FFFFFFF;
       for (int ci = 0; ci < nc; ++ci) {
-        // No element scores above (value of the row's maximum) / T + its own Gumbel term g = -log(-log u),
-        // and -log u >= 1 - u: with cb a score that some kept element of the row reaches, an element
-        // with 1 - u > eps = exp(-(cb - xtop - margin)) has g < cb - xtop - margin.
+        // the best score known so far, less twice the screening slack (see st_final_chunk)
         const float cb = key_f32(ctl.best_key);
-        const float eps = expf(-(cb - 2.0f * (kGumbelSlack + 1e-5f * fabsf(cb)) - xtop)) * 1.000001f;
+        const float cbm = cb - 2.0f * (kGumbelSlack + 1e-5f * fabsf(cb));
         const bool arrived = mbar_wait_suspended(&ctl.mbar[slot], phase);
         const unsigned char* buf = ring + (size_t)slot * kStChunk;
         const int elem0 = part * kStFinalElems + ci * kStFinalChunkElems;
         if (res >= 0 && !(p.debug & 1)) {
           const int ngroups = ci != nc - 1 || last_elems >= kStFinalChunkElems ? kStFinalChunkElems / 8 : (int)(last_elems >> 3);
-          st_final_chunk(buf, ngroups, elem0, tv2, tvf, inv_T, eps, a1, a2, u1, b1, t1);
+          st_final_chunk(buf, ngroups, elem0, tv2, tvf, inv_T, cbm, a1, a2, u1, b1, t1);
         }
         if (a1 > published) { atomicMax(&ctl.best_key, f32_key(a1)); published = a1; }
         if (__syncthreads_or(!arrived)) {
