@@ -109,15 +109,15 @@ int tlx_sort(void* stream, const void* keys, int dtype, int64_t rows, int64_t n,
 
 /* ---- sort without any allocation ------------------------------------------------
  * Same operation and results as tlx_sort, for callers that have nowhere to get scratch
- * memory from: code running inside a CUDA-graph capture or a stream callback chain, plugin
- * hosts whose memory pool is owned by another runtime, or processes that were handed a fixed
- * memory budget and must not call cudaMalloc (nor have the library call it for them).  The
+ * memory from: plugin hosts whose memory pool is owned by another runtime, or processes that
+ * were handed a fixed memory budget and must not call cudaMalloc (nor have the library call it
+ * for them).  The
  * scratch of the multi-tile path is a fixed area inside the library image (16 MiB, reported by
  * tlx_sort_static_max_bytes; every GPU that loads the library holds it until exit).
  *   - rows whose composites need more than that are rejected with TLX_ERR_INVALID and a
  *     message; nothing is launched;
  *   - the first call on a device looks up the area's device address (with that device
- *     current); make that first call before any stream capture;
+ *     current), a host-side query; later calls only launch kernels;
  *   - all calls share the one area and it keeps the previous call's contents; the kernels
  *     write every entry before reading it, so nothing needs clearing, but two calls that
  *     overlap on the GPU (different streams) race: serialise them;

@@ -1,7 +1,7 @@
 """The allocation-free sort entry point against the regular one.
 
 tlx_sort_static is for callers that cannot provide scratch memory (no cudaMalloc allowed in
-their position: inside a captured stream, under a foreign memory pool, or on a fixed budget);
+their position: under a foreign memory pool, or on a fixed budget);
 it keeps the scratch in a fixed area inside the library.  It must give exactly what tlx_sort
 gives, call after call, since every call reuses the same area.
 """
