@@ -1067,7 +1067,7 @@ __device__ __forceinline__ int st_finish_normal(const StreamParams& p, int row, 
     // The fetched slots, dealt evenly to the threads (a slot is an entry if its index is below its segment's
     // count).  Rolled on purpose, as are the loops below: this code runs once per CTA, so the time goes into
     // fetching its instructions, not into executing them.
-#pragma unroll 1
+#pragma unroll 2
     for (int i = threadIdx.x; i < nseg * kStSpec; i += kStThreads) {
       const int s2 = i / kStSpec, idx = i % kStSpec;
       if (idx < t.segcnt[s2]) tl_place(t, p, d, noise_row, t.raw[i], s2, t.segoff[s2] + idx, mymax, over);
