@@ -1949,7 +1949,7 @@ static size_t counters_bytes(int64_t rows) { return 256 + (((size_t)rows * sizeo
 // ---- streaming path (sampler_stream.cuh): workspace layout and launches ---------------------------
 struct StreamLayout {
   int P, part_chunks, nchunks, nfin;
-  size_t off_desc, off_counts, off_lump, off_flag, off_rowdone, off_state, off_records, off_hist, off_cands, off_timeline = 0, bytes;
+  size_t off_desc, off_counts, off_lump, off_wbest, off_flag, off_rowdone, off_state, off_records, off_hist, off_cands, off_timeline = 0, bytes;
 };
 static size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 static StreamLayout stream_layout(int64_t rows, int64_t vocab) {
@@ -1963,6 +1963,7 @@ static StreamLayout stream_layout(int64_t rows, int64_t vocab) {
   l.off_desc = o;    o = align256(o + (size_t)rows * sizeof(StreamDesc));
   l.off_counts = o;  o = align256(o + (size_t)rows * l.P * kStWarps * sizeof(int));
   l.off_lump = o;    o = align256(o + (size_t)rows * l.P * sizeof(double));
+  l.off_wbest = o;   o = align256(o + (size_t)rows * sizeof(unsigned long long));
   l.off_flag = o;    o = align256(o + (size_t)rows * sizeof(int));
   l.off_rowdone = o; o = align256(o + (size_t)rows * sizeof(int));
   l.off_state = o;   o = align256(o + (size_t)rows * sizeof(WideState));
@@ -2077,6 +2078,7 @@ static int launch_stream_path(cudaStream_t st, const SampleParams& sp, void* wor
   p.desc = (StreamDesc*)(ws + l.off_desc);
   p.counts = (int*)(ws + l.off_counts);
   p.wlump = (double*)(ws + l.off_lump);
+  p.wbest = (unsigned long long*)(ws + l.off_wbest);
   p.wflag = (int*)(ws + l.off_flag);
   p.rowdone = (int*)(ws + l.off_rowdone);
   p.wstate = (WideState*)(ws + l.off_state);

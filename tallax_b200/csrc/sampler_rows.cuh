@@ -702,9 +702,10 @@ __global__ void __launch_bounds__(kRwThreads, 2) sample_rows_stream_kernel(RowsP
       const float nxl = -xref * 1.44269504f;
       float lump = 0.f;
       int above = 0;
+      uint32_t dmin = 0xFFFFFFFFu;   // (the greatest element's position is not used on this path)
       ok = rw_pass(p, rowp, sm, phases, true, [&](const unsigned char* buf, int nvec, int, bool full) {
-        if (full) st_hist_chunk<true, kRwThreads, kRwVecPerThread>(buf, nvec, key16, nxl, sm.hist, lump, above);
-        else st_hist_chunk<false, kRwThreads, kRwVecPerThread>(buf, nvec, key16, nxl, sm.hist, lump, above);
+        if (full) st_hist_chunk<true, kRwThreads, kRwVecPerThread>(buf, nvec, key16, nxl, sm.hist, lump, above, 0, dmin);
+        else st_hist_chunk<false, kRwThreads, kRwVecPerThread>(buf, nvec, key16, nxl, sm.hist, lump, above, 0, dmin);
       });
       primed = false;
       TLX_STAMP(sp, 2);

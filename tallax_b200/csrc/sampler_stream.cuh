@@ -83,9 +83,11 @@ struct __align__(16) WideState {
   int result;                // kWideNotReady until the row's threshold is settled; then -1 (the window did not
                              // settle it) or (key of the greatest element - threshold key) << 16 | threshold key:
                              // an element is kept if its value is not below the value of the threshold key
+  uint32_t best_key;         // best screened score of a kept element of the row known so far (ordered key):
+                             // seeded with the score of the row's greatest element when the threshold is
+                             // published (one 8-byte store with `result`), raised by the final items
   int parts_done;            // stream kernel: parts of the row whose totals are in
-  int done;                  // final pass of the finish kernel: ranges that have delivered their record
-  uint32_t best_key;         // final items of the stream kernel: best screened score of the row so far (ordered key)
+  int done;                  // final items (stream kernel) or ranges (finish kernel) that have delivered their record
 };
 static_assert(sizeof(WideState) == 16, "WideState layout");
 constexpr int kWideNotReady = (int)0x80000000;
@@ -115,6 +117,7 @@ struct StreamParams {
   uint32_t* cands;       // [rows * P * 8 * kStWarpCap] bf16 bits << 16 | position inside the part
   uint32_t* whist;       // [rows * kStWin] wide rows: window histogram, bin = window top - key16
   double* wlump;         // [rows * P] wide rows: sum of exp(x - xref) below the window
+  unsigned long long* wbest;   // [rows] wide rows: (window top - key of the greatest element) << 32 | its token
   int* wflag;            // [rows] wide rows: an element lay above the window
   WideState* wstate;     // [rows]
   FinRecord* records;    // [rows * nfin]
@@ -378,6 +381,7 @@ __global__ void __launch_bounds__(kStProThreads) sample_prologue_kernel(StreamPa
       for (int i = threadIdx.x; i < kStWin / 4; i += kStProThreads) wh[i] = make_uint4(0, 0, 0, 0);
       if (threadIdx.x == 0) {
         p.wflag[row] = 0;
+        p.wbest[row] = ~0ull;
         WideState ws{};
         ws.result = kWideNotReady;
         ws.best_key = f32_key(-INFINITY);
@@ -449,7 +453,7 @@ __device__ __forceinline__ void st_filter_chunk(const unsigned char* buf, int nv
 // No branches: every element computes its bin and its exp; predicates pick what is used.
 template <bool kFull, int NT = kStThreads, int VPT = kStVecPerThread>
 __device__ __forceinline__ void st_hist_chunk(const unsigned char* buf, int nvec, int wtop, float nxl, uint32_t* win,
-                                              float& lump, int& above) {
+                                              float& lump, int& above, int pos0, uint32_t& dmin) {
 #pragma unroll 1
   for (int j = 0; j < VPT; ++j) {
     const int v = (int)threadIdx.x + j * NT;
@@ -469,6 +473,7 @@ __device__ __forceinline__ void st_hist_chunk(const unsigned char* buf, int nvec
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         above |= d[e];
+        dmin = min(dmin, ((uint32_t)d[e] << 16) | (uint32_t)(pos0 + v * 8 + e));   // greatest key, with its position
         if ((unsigned)d[e] < (unsigned)kStWin) atomicAdd(&win[d[e]], 1u);
         lump += d[e] >= kStWin ? val[e] : 0.f;
       }
@@ -744,17 +749,17 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         const long long tl_f0 = global_timer_ns();
         if (p.sp.timeline && p.sp.timeline[(size_t)blockIdx.x * 16 + 13] == 0) p.sp.timeline[(size_t)blockIdx.x * 16 + 13] = tl_f0;
 #endif
-        volatile int* rp = &p.wstate[row].result;
-        const float T_ = p.sp.temperature[row];                                             // one round trip
-        const uint32_t bk = *reinterpret_cast<volatile uint32_t*>(&p.wstate[row].best_key);  // for all three
-        int res = *rp;
-        for (int spin = 0; res == kWideNotReady && spin < (1 << 16); ++spin) {
+        volatile unsigned long long* rp = reinterpret_cast<volatile unsigned long long*>(&p.wstate[row]);
+        const float T_ = p.sp.temperature[row];   // one round trip for both loads
+        unsigned long long w = *rp;               // result and best score, published as one word
+        for (int spin = 0; (int)(uint32_t)w == kWideNotReady && spin < (1 << 16); ++spin) {
           __nanosleep(64);
-          res = *rp;
+          w = *rp;
         }
+        int res = (int)(uint32_t)w;
         if (res == kWideNotReady) { *p.error_flag = 1; res = -1; }
         ctl.fin_result = res;
-        ctl.best_key = bk;
+        ctl.best_key = (uint32_t)(w >> 32);
         ctl.fin_T = T_;
 #ifdef TLX_TIMELINE
         if (p.sp.timeline) { p.sp.timeline[(size_t)blockIdx.x * 16 + 12] += 1; p.sp.timeline[(size_t)blockIdx.x * 16 + 14] += global_timer_ns() - tl_f0; }
@@ -842,6 +847,7 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
     int wc = 0;
     float lump = 0.f;
     int above = 0;
+    uint32_t dmin = 0xFFFFFFFFu;   // wide rows: (window top - key) << 16 | position in the part, of the greatest element
     if (cls == kStWide) {
       for (int i = threadIdx.x; i < kStWin; i += kStThreads) area[i] = 0;
       __syncthreads();
@@ -856,8 +862,8 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         if (full) st_filter_chunk<true>(buf, kStChunkVecs, ci * kStChunkElems, tvf, tv2, dst, wc, wl);
         else st_filter_chunk<false>(buf, last_nvec, ci * kStChunkElems, tvf, tv2, dst, wc, wl);
       } else if (cls == kStWide) {
-        if (full) st_hist_chunk<true>(buf, kStChunkVecs, key16, nxl, area, lump, above);
-        else st_hist_chunk<false>(buf, last_nvec, key16, nxl, area, lump, above);
+        if (full) st_hist_chunk<true>(buf, kStChunkVecs, key16, nxl, area, lump, above, ci * kStChunkElems, dmin);
+        else st_hist_chunk<false>(buf, last_nvec, key16, nxl, area, lump, above, ci * kStChunkElems, dmin);
       }
       if (__syncthreads_or(!arrived)) {   // a copy never arrived: give up, the finish kernel reports it
         if (threadIdx.x == 0) *p.error_flag = 1;
@@ -882,13 +888,18 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
       double l = (double)lump;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) l += shfl_xor_f64(l, o);
-      if (lane == 0) ctl.dsum[warp] = l;
+      dmin = __reduce_min_sync(0xFFFFFFFFu, dmin);
+      if (lane == 0) { ctl.dsum[warp] = l; ctl.wkey[warp] = dmin; }
       if (above < 0) p.wflag[row] = 1;
       __syncthreads();   // with thread 0's fence below: every thread's additions come before the count
       if (threadIdx.x == 0) {
         double t = 0.0;
         for (int w = 0; w < kStWarps; ++w) t += ctl.dsum[w];
         p.wlump[(size_t)row * p.P + part] = t;
+        uint32_t dm = ctl.wkey[0];
+        for (int w = 1; w < kStWarps; ++w) dm = min(dm, ctl.wkey[w]);
+        atomicMin(&p.wbest[row], ((unsigned long long)(dm >> 16) << 32) |
+                                     (unsigned long long)((uint32_t)part * (uint32_t)(p.part_chunks * kStChunkElems) + (dm & 0xFFFFu)));
         __threadfence();
         ctl.flag = atomicAdd(&p.wstate[row].parts_done, 1) == p.P - 1;
       }
@@ -904,7 +915,22 @@ __global__ void __launch_bounds__(kStThreads, 4) sample_stream_kernel(StreamPara
         if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 10] = global_timer_ns() - tl_t;
 #endif
         const int v = st_wide_threshold(p, row, key16, p.sp.top_p[row], area, ctl.wide);
-        if (threadIdx.x == 0) *reinterpret_cast<volatile int*>(&p.wstate[row].result) = wide_result(ctl.wide.kmax16, v);
+        if (threadIdx.x == 0) {
+          // The row's greatest element is always kept: its screened score (the very expression its final item
+          // will evaluate) seeds the row's best score, so that the final items' test bites from their first
+          // chunk on.  Threshold and seed become visible together (one 8-byte store).
+          uint32_t seed = f32_key(-INFINITY);
+          const unsigned long long wb = __ldcg(&p.wbest[row]);
+          const int64_t pos = (int64_t)(uint32_t)wb;
+          const float T_ = p.sp.temperature[row];
+          if (v >= 0 && p.fin_items > 0 && pos < p.sp.vocab && (wb >> 32) < 65536ull) {
+            const uint32_t bits = reinterpret_cast<const unsigned short*>(p.sp.logits)[(int64_t)row * p.sp.row_stride + pos];
+            const float u = p.sp.noise.at(row + p.sp.dim0_offset, pos);
+            seed = f32_key(fmaf(__uint_as_float(bits << 16), 1.0f / T_, gumbel_screen(u)));
+          }
+          const unsigned long long word = ((unsigned long long)seed << 32) | (unsigned long long)(uint32_t)wide_result(ctl.wide.kmax16, v);
+          *reinterpret_cast<volatile unsigned long long*>(&p.wstate[row]) = word;
+        }
 #ifdef TLX_TIMELINE
         if (threadIdx.x == 0 && p.sp.timeline) p.sp.timeline[(size_t)blockIdx.x * 16 + 11] = global_timer_ns() - tl_t;
 #endif
