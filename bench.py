@@ -507,8 +507,10 @@ def run_op_workload(args):
 
 def vocab_sharded_record(args, torch, dist, device, rank, world, steps=30):
     """Configuration 5: bf16 [1024, 151936] sharded along the vocabulary over the ranks (strong scaling).
-    One step = local top-k' per shard, NCCL all-gather of the candidates, merge and sample.  Returns the
-    record on rank 0, None elsewhere.  The process group (if world > 1) is the caller's."""
+    One step = local top-k' per shard, exchange of the candidates, merge and sample.  The exchange is timed
+    both ways: done by the candidate kernel over peer memory (the record's headline) and as an NCCL all-gather
+    between the two kernels.  Returns the record on rank 0, None elsewhere.  The process group (if world > 1)
+    is the caller's."""
     from tallax_b200 import _lib, sampling
     lib = _lib.load()
     rows, vocab, k = 1024, 151936, 50
@@ -527,12 +529,10 @@ def vocab_sharded_record(args, torch, dist, device, rank, world, steps=30):
                                    top_p=torch.full((rows,), 0.95, device=device),
                                    temperature=torch.full((rows,), 0.8, device=device))
     vws = sampling.VocabShardedWorkspace(rows, k, world, device)
+    exchange = sampling.make_vocab_exchange(rows, k, device=device)     # a collective; ends with a barrier
     mismatches = None
     if rank == 0:
         whole = sampling.sample(None, x[:, :vl * world], md, noise=noise[:, :vl * world]).clone()
-    tok = sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws)
-    if rank == 0:
-        mismatches = int((whole != tok).sum())
     del x, noise
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)   # > 126 MB L2
 
@@ -541,26 +541,68 @@ def vocab_sharded_record(args, torch, dist, device, rank, world, steps=30):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws)
-    barrier()
-    total = 0.0
-    launches0 = lib.tlx_kernel_launches()
-    with ClockSampler(device.index) as clocks:
+    def step_gathered():
+        return sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws)
+
+    def step_exchange():
+        return sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws,
+                                             exchange=exchange)
+
+    def timed(step):
+        """(ms per step as the max over ranks, clock summary, launches, tokens of the first call)"""
+        tok = step().clone()
+        for _ in range(max(args.warmup, 3)):
+            step()
+        barrier()
+        total = 0.0
+        launches0 = lib.tlx_kernel_launches()
+        with ClockSampler(device.index) as clocks:
+            for i in range(steps):
+                flush.fill_(i & 0xFF)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                step()
+                e1.record()
+                e1.synchronize()
+                total += e0.elapsed_time(e1)
+        launches = lib.tlx_kernel_launches() - launches0
+        t = torch.tensor([total], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps, clocks, int(launches), tok
+
+    # the step as a CUDA graph of the two kernels (the exchange path has no collective call to capture)
+    def timed_graph():
+        graph = torch.cuda.CUDAGraph()
+        barrier()
+        with torch.cuda.graph(graph):
+            step_exchange()
+        barrier()
+        total = 0.0
         for i in range(steps):
             flush.fill_(i & 0xFF)
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            sampling.sample_vocab_sharded(None, shard, md, noise_shard=nshard, k_cand=k, workspace=vws)
+            graph.replay()
             e1.record()
             e1.synchronize()
             total += e0.elapsed_time(e1)
-    launches = lib.tlx_kernel_launches() - launches0
-    t = torch.tensor([total], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / steps
+        t = torch.tensor([total], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
+
+    ms_g, _, launches_g, tok_g = timed(step_gathered)
+    ms, clocks, launches, tok = timed(step_exchange)
+    ms_graph = timed_graph()
+    ex_steps, ex_error = exchange.state()
+    barrier()
+    if rank == 0:
+        mismatches = int((whole != tok).sum())
+        mismatches_g = int((whole != tok_g).sum())
+    exchange.close()
     if rank != 0:
         return None
     peak, peak_src = peaks()
@@ -571,15 +613,21 @@ def vocab_sharded_record(args, torch, dist, device, rank, world, steps=30):
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "c5: bf16 [1024,151936] = N(0,2) + 4*rank^-1.1, T=0.8, top_k=50, top_p=0.95, "
-                               "vocab split over the ranks, k'=50 candidates per shard, NCCL all-gather",
+                               "vocab split over the ranks, k'=50 candidates per shard, stored by the candidate "
+                               "kernel into every rank's exchange buffer over NVLink; the merge kernel waits per row",
                    "l2": "256 MB flush buffer written between steps"},
         "clocks": clocks.summary(), "gpu_launches": int(launches),
         "mismatches": mismatches,
         "parity": f"{mismatches} of {rows} tokens differ from the unsharded fused sampler on rank 0",
+        "exchange_state": {"steps": ex_steps, "error": ex_error},
+        "graph_replay_ms_per_step": ms_graph,
+        "nccl_all_gather": {"ms_per_step": ms_g, "gpu_launches": launches_g, "mismatches": mismatches_g,
+                            "note": "the same step with torch.distributed all_gather_into_tensor between the two "
+                                    "kernels"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": peak_src,
                      "note": "per GPU: its logits slice once + candidates, over the whole step "
-                             "(shard kernel, all-gather, merge kernel)"}}
+                             "(candidate kernel with the exchange, merge kernel)"}}
 
 
 def run_vocab_sharded(args):

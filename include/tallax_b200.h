@@ -263,6 +263,46 @@ int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* ca
                          int64_t block_stride, int64_t row_stride, const int32_t* top_k,
                          const float* top_p, const float* temperature, int32_t* out_tokens);
 
+/* ---- vocab-sharded sampler, candidates exchanged over peer memory ------------------
+ * The all-gather between the two stages (jax.lax.all_gather in tallax/_src/sampling.py:312-316)
+ * done by the stage-1 kernel itself: every rank owns an exchange buffer (tlx_exchange_bytes, the
+ * same rows, k_cand and world on every rank) and maps the other ranks' buffers; rank s stores each
+ * row's candidates into slot s of every rank's buffer over NVLink and counts the row's arrival
+ * there; the stage-2 kernel of a rank waits per row (bounded: two seconds, then the buffer's error
+ * word and *out_status are set and the row is merged as it is) until all `world` blocks have
+ * arrived.  No collective and no host synchronisation between the two calls.  Every rank makes the
+ * same sequence of calls (one tlx_exchange_shard_candidates, then one
+ * tlx_exchange_merge_and_sample, per step); the ranks must have finished creating and mapping
+ * the buffers (a host barrier) before the first step.  After a wait gave up the buffers are out
+ * of step: destroy and recreate them.
+ *
+ * tlx_exchange_create allocates and clears this rank's buffer (the one allocation the library makes:
+ * an inter-process handle covers a whole device allocation) and writes its handle, which the other
+ * processes pass to tlx_exchange_open; in one process with several devices, or to stand in for
+ * several ranks on one device, plain pointers serve and no handle is needed (ipc_handle NULL).
+ * `exchange_of_rank` is a HOST array of `world` device pointers, [rank] this rank's own buffer.
+ * The other arguments are those of tlx_shard_candidates / _dev (key_dev NULL: key0, key1;
+ * dim0_offset_dev NULL: dim0_offset) and tlx_merge_and_sample.  world <= 16.           */
+#define TLX_EXCHANGE_HANDLE_BYTES 64
+size_t tlx_exchange_bytes(int64_t rows, int k_cand, int world);
+int tlx_exchange_create(int64_t rows, int k_cand, int world, void** exchange,
+                        unsigned char* ipc_handle /* TLX_EXCHANGE_HANDLE_BYTES, or NULL */);
+int tlx_exchange_open(const unsigned char* ipc_handle, void** exchange);
+int tlx_exchange_close(void* exchange);      /* a buffer mapped by tlx_exchange_open */
+int tlx_exchange_destroy(void* exchange);    /* a buffer made by tlx_exchange_create */
+int tlx_exchange_status(void* stream, const void* exchange, uint32_t* steps, uint32_t* error);
+int tlx_exchange_shard_candidates(void* stream, const void* logits, int dtype, int64_t rows,
+                                  int64_t v_local, int64_t row_stride, int64_t col_offset,
+                                  int k_cand, const float* noise, int64_t noise_stride,
+                                  const uint32_t* key_dev, uint32_t key0, uint32_t key1,
+                                  int64_t vocab_total, int64_t dim0_offset,
+                                  const int32_t* dim0_offset_dev, int rank, int world,
+                                  void* const* exchange_of_rank);
+int tlx_exchange_merge_and_sample(void* stream, void* exchange, int64_t rows, int k_cand,
+                                  int world, const int32_t* top_k, const float* top_p,
+                                  const float* temperature, int32_t* out_tokens,
+                                  int32_t* out_status /* nullable */);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,15 @@ SIGNATURES = {
     "tlx_shard_candidates": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _u32, _u32, _i64, _i64,
                                     _vp, _vp, _vp, _vp, _sz]),
     "tlx_merge_and_sample": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i32, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "tlx_exchange_bytes": (_sz, [_i64, _i32, _i32]),
+    "tlx_exchange_create": (_i32, [_i64, _i32, _i32, _vp, _vp]),
+    "tlx_exchange_open": (_i32, [_vp, _vp]),
+    "tlx_exchange_close": (_i32, [_vp]),
+    "tlx_exchange_destroy": (_i32, [_vp]),
+    "tlx_exchange_status": (_i32, [_vp, _vp, _vp, _vp]),
+    "tlx_exchange_shard_candidates": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _i64, _vp, _u32, _u32,
+                                             _i64, _i64, _vp, _i32, _i32, _vp]),
+    "tlx_exchange_merge_and_sample": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
 }
 
 _lib = None

@@ -357,3 +357,117 @@ def merge_and_sample(gathered, top_k_, top_p, temperature, out=None):
         n_shards * k, k, block, k, _ptr(_i32vec(top_k_, rows, dev)), _ptr(_f32vec(top_p, rows, dev)),
         _ptr(_f32vec(temperature, rows, dev)), _ptr(out)))
     return out
+
+
+# ---- vocab-sharded sampler with the candidates exchanged over peer memory ------------------------------
+class Exchange:
+    """This rank's exchange buffer and the other ranks' buffers as mapped here (C ABI: tlx_exchange_*).
+
+    `Exchange.create(rows, k_cand, world)` allocates the local buffer and returns it with its 64-byte
+    inter-process handle; `attach(rank, handles)` maps the other ranks' buffers from their handles.
+    `Exchange.local_group(rows, k_cand, world)` makes `world` buffers in this process (several ranks stood
+    in for by one device, or one process driving several devices)."""
+
+    def __init__(self, rows, k_cand, world):
+        self.rows, self.k_cand, self.world = int(rows), int(k_cand), int(world)
+        self.rank = None
+        self.own = None          # device address of this rank's buffer
+        self.handle = None
+        self.peers = None        # ctypes array of `world` device addresses
+        self._opened = []
+        self.status = None
+
+    @classmethod
+    def create(cls, rows, k_cand, world, device=None):
+        import ctypes
+        self = cls(rows, k_cand, world)
+        buf = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        with torch.cuda.device(dev):
+            check(_lib.load().tlx_exchange_create(self.rows, self.k_cand, self.world, ctypes.byref(buf), handle))
+            self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.device = dev
+        self.own = buf.value
+        self.handle = bytes(handle)
+        return self
+
+    def attach(self, rank, handles):
+        """handles: the `world` ranks' handles in rank order (this rank's own entry is not opened)."""
+        import ctypes
+        assert len(handles) == self.world
+        self.rank = int(rank)
+        ptrs = []
+        with torch.cuda.device(self.device):
+            for i, h in enumerate(handles):
+                if i == self.rank:
+                    ptrs.append(self.own)
+                    continue
+                peer = ctypes.c_void_p()
+                hb = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                check(_lib.load().tlx_exchange_open(hb, ctypes.byref(peer)))
+                self._opened.append(peer.value)
+                ptrs.append(peer.value)
+        self.peers = (ctypes.c_void_p * self.world)(*ptrs)
+        return self
+
+    @classmethod
+    def local_group(cls, rows, k_cand, world, device=None):
+        import ctypes
+        group = [cls.create(rows, k_cand, world, device) for _ in range(world)]
+        for r, e in enumerate(group):
+            e.rank = r
+            e.peers = (ctypes.c_void_p * world)(*[g.own for g in group])
+        return group
+
+    def state(self):
+        """(steps completed, error word) of this rank's buffer; synchronises the current stream."""
+        import ctypes
+        steps, err = ctypes.c_uint32(), ctypes.c_uint32()
+        check(_lib.load().tlx_exchange_status(_stream(), self.own, ctypes.byref(steps), ctypes.byref(err)))
+        return steps.value, err.value
+
+    def close(self):
+        lib = _lib.load()
+        for p in self._opened:
+            lib.tlx_exchange_close(p)
+        self._opened = []
+        if self.own:
+            lib.tlx_exchange_destroy(self.own)
+            self.own = None
+
+
+def exchange_shard_candidates(logits_shard, col_offset: int, exchange: Exchange, *, noise_shard=None, rng_key=None,
+                              vocab_total=None, dim0_offset=0):
+    """Stage 1 with the exchange fused in: this rank's top-k' of every row goes straight into every rank's
+    exchange buffer."""
+    logits_shard = _dev(logits_shard)
+    rows, v_local = logits_shard.shape
+    dev = logits_shard.device
+    if (rows, ) != (exchange.rows, ):
+        raise ValueError("exchange was made for another row count")
+    if noise_shard is not None:
+        noise_shard = _dev(noise_shard)
+    elif rng_key is None:
+        raise ValueError("either rng_key or noise_shard is required")
+    kd, od = key_operand(rng_key), offset_operand(dim0_offset)
+    k0 = k1 = 0
+    if kd is None and noise_shard is None:
+        k0, k1 = key_pair(rng_key)
+    check(_lib.load().tlx_exchange_shard_candidates(
+        _stream(), _ptr(logits_shard), dtype_code(logits_shard), rows, v_local, v_local, int(col_offset),
+        exchange.k_cand, _ptr(noise_shard), noise_shard.shape[1] if noise_shard is not None else 0, _ptr(kd), k0, k1,
+        int(vocab_total if vocab_total is not None else v_local), 0 if od is not None else int(dim0_offset), _ptr(od),
+        exchange.rank, exchange.world, exchange.peers))
+
+
+def exchange_merge_and_sample(exchange: Exchange, top_k_, top_p, temperature, out=None):
+    """Stage 2 on this rank's exchange buffer: waits per row for all ranks' candidates, merges, samples."""
+    rows = exchange.rows
+    dev = exchange.device
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=dev)
+    check(_lib.load().tlx_exchange_merge_and_sample(
+        _stream(), exchange.own, rows, exchange.k_cand, exchange.world, _ptr(_i32vec(top_k_, rows, dev)),
+        _ptr(_f32vec(top_p, rows, dev)), _ptr(_f32vec(temperature, rows, dev)), _ptr(out), _ptr(exchange.status)))
+    return out

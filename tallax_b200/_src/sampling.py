@@ -65,8 +65,27 @@ class VocabShardedWorkspace:
         self.tokens = torch.empty(rows, dtype=torch.int32, device=device)
 
 
+def make_vocab_exchange(rows: int, k_cand: int, group=None, device=None):
+    """This rank's exchange buffer for `sample_vocab_sharded(..., exchange=...)`, with the other ranks' buffers
+    mapped: every rank of `group` calls it with the same `rows` and `k_cand` (a collective: the handles are
+    all-gathered and a barrier ends it).  Keep it for the life of the decode loop; `.close()` frees it."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    ex = ops.Exchange.create(rows, k_cand, world, device)
+    handles = [None] * world
+    if world > 1:
+        dist.all_gather_object(handles, ex.handle, group=group)
+    else:
+        handles = [ex.handle]
+    ex.attach(rank, handles)
+    if world > 1:
+        dist.barrier(group=group)
+    return ex
+
+
 def sample_vocab_sharded(rng_key, logits_shard, tpu_sampling_metadata, *, group=None, noise_shard=None,
-                         k_cand: int | None = None, dim0_offset: int = 0, workspace=None):
+                         k_cand: int | None = None, dim0_offset: int = 0, workspace=None, exchange=None):
     """Sampler for logits sharded along the vocabulary across the ranks of `group`
     (the shard-mapped body of sampling.py:300-321): local top-k' on this rank's
     contiguous slice, one all-gather of the (value, global token, noise) candidates,
@@ -74,6 +93,10 @@ def sample_vocab_sharded(rng_key, logits_shard, tpu_sampling_metadata, *, group=
 
     Needs 1 <= top_k <= k_cand for every row (the reference fixes k' = 128).
     One library call per stage; with `workspace` (a VocabShardedWorkspace) nothing is allocated.
+
+    With `exchange` (from `make_vocab_exchange`) there is no collective call: the candidate kernel stores
+    every row's block into all ranks' exchange buffers over NVLink and the merge kernel waits per row for
+    the blocks to arrive.  `workspace.tokens`, when given, receives the result.
     """
     import torch.distributed as dist
 
@@ -81,6 +104,13 @@ def sample_vocab_sharded(rng_key, logits_shard, tpu_sampling_metadata, *, group=
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     rows, v_local = logits_shard.shape
+    if exchange is not None:
+        if exchange.world != world or exchange.rank != rank:
+            raise ValueError("exchange was made for another group")
+        ops.exchange_shard_candidates(logits_shard, rank * v_local, exchange, noise_shard=noise_shard, rng_key=rng_key,
+                                      vocab_total=v_local * world, dim0_offset=dim0_offset)
+        return ops.exchange_merge_and_sample(exchange, md.top_k, md.top_p, md.temperature,
+                                             out=workspace.tokens if workspace is not None else None)
     if k_cand is None:
         k_cand = 128
     k_cand = min(k_cand, v_local)

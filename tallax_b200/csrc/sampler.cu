@@ -46,6 +46,7 @@
 #include <mutex>
 
 #include "sampler_general.cuh"
+#include "exchange.cuh"
 
 namespace tlx {
 
@@ -1761,34 +1762,169 @@ __global__ void __launch_bounds__(256) top_p_and_sample_kernel(const typename El
 constexpr int kMergeThreads = 512;
 constexpr int kMergeMaxCand = 8192;
 
-__global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(
-    const float* __restrict__ cand_vals, const int32_t* __restrict__ cand_idx, const float* __restrict__ cand_noise,
-    int n_cand, int k_per_block, int64_t block_stride, int64_t row_stride, const int32_t* __restrict__ top_k,
-    const float* __restrict__ top_p, const float* __restrict__ temperature, int32_t* __restrict__ out) {
+struct MergeParams {
+  const float* cand_vals;
+  const int32_t* cand_idx;
+  const float* cand_noise;
+  int n_cand, k_per_block;
+  int64_t block_stride, row_stride;
+  const int32_t* top_k;
+  const float* top_p;
+  const float* temperature;
+  int32_t* out;
+  // exchange mode (xbuf non-null): the candidates are read from this rank's exchange buffer, set by set
+  unsigned char* xbuf;
+  size_t off_flags[2], off_cand[2];
+  int world;
+  int64_t rows;
+  int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Number of entries of the ascending list blk[0..len) that are smaller than c.
+__device__ __forceinline__ int count_below(const uint64_t* blk, int len, uint64_t c) {
+  int lo = 0;
+  while (len > 0) {
+    const int half = len >> 1;
+    if (blk[lo + half] < c) { lo += half + 1; len -= half + 1; }
+    else len = half;
+  }
+  return lo;
+}
+
+// One CTA per row.  The shards' blocks arrive sorted (value desc, token asc), which the kernel checks: a
+// few blocks and a small K are merged by one warp (a head per lane, the least of them K times); otherwise a
+// candidate's place in the merged order is its place in its own block plus, for every other block, the
+// number of entries that precede it there (a binary search), and only places below K are filled.
+// Unsorted blocks take the bitonic network over all candidates instead.
+__global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergeParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
+  const int n_cand = p.n_cand, kpb = p.k_per_block;
+  int P = 2;
+  while (P < n_cand) P <<= 1;
+  uint64_t* merged = cand + P;
   const int64_t r = blockIdx.x;
-  const float* v = cand_vals + r * row_stride;
-  const int32_t* id = cand_idx + r * row_stride;
-  const float* un = cand_noise + r * row_stride;
-  auto at = [&](uint32_t i) { return (int64_t)(i / k_per_block) * block_stride + (int64_t)(i % k_per_block); };
+
+  const float* v = p.cand_vals;
+  const int32_t* id = p.cand_idx;
+  const float* un = p.cand_noise;
+  ExchangeHeader* xh = reinterpret_cast<ExchangeHeader*>(p.xbuf);
+  uint32_t* flag = nullptr;
+  if (xh) {
+    const uint32_t par = *reinterpret_cast<volatile const uint32_t*>(&xh->step) & 1u;
+    const size_t plane = (size_t)p.rows * kpb;
+    v = reinterpret_cast<const float*>(p.xbuf + p.off_cand[par]);
+    id = reinterpret_cast<const int32_t*>(v) + plane;
+    un = v + 2 * plane;
+    flag = reinterpret_cast<uint32_t*>(p.xbuf + p.off_flags[par]) + r;
+    if (threadIdx.x == 0) {
+      // every rank's block of this row has arrived when the word reads `world`; two seconds at most
+      const unsigned long long t0 = global_timer_ns();
+      bool ok = false;
+      for (int it = 0; it < (1 << 24); ++it) {
+        if (ld_acquire_sys_u32(flag) >= (uint32_t)p.world) { ok = true; break; }
+        if (global_timer_ns() - t0 > 2000000000ull) break;
+        __nanosleep(100);
+      }
+      if (!ok) {
+        atomicExch(&xh->error, 1u);
+        if (p.status) atomicExch(p.status, 1);
+      }
+    }
+    __syncthreads();
+  }
+  v += r * p.row_stride;
+  id += r * p.row_stride;
+  un += r * p.row_stride;
+  auto at = [&](uint32_t i) { return (int64_t)(i / kpb) * p.block_stride + (int64_t)(i % kpb); };
   // low word = position in the gathered list: shards are laid side by side in ascending
   // token order, so position order equals token order among equal values
-  for (int i = threadIdx.x; i < n_cand; i += blockDim.x) cand[i] = cand_make(f32_key(v[at(i)]), (uint32_t)i);
-  __syncthreads();
-  sort_candidates(cand, n_cand);
-  int K = top_k[r];
-  if (K <= 0 || K > n_cand) K = n_cand;
-  const float T_ = temperature[r];
-  if (T_ < kSamplingEps) {
-    if (threadIdx.x == 0) out[r] = id[at(cand_low(cand[0]))];
-    return;
+  int unsorted = 0;
+  for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
+    const float x = xh ? __ldcg(v + at(i)) : v[at(i)];
+    cand[i] = cand_make(f32_key(x), (uint32_t)i);
   }
-  const int tok = sample_tail<2>(
-      K, top_p[r], T_, s, [&](int i) { return key_f32(cand_key(cand[i])); },
-      [&](int i) { return (int)id[at(cand_low(cand[i]))]; }, [&](int i) { return un[at(cand_low(cand[i]))]; });
-  if (threadIdx.x == 0) out[r] = tok;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_cand; i += blockDim.x)
+    if (i % kpb && cand[i - 1] > cand[i]) unsorted = 1;
+  unsorted = __syncthreads_or(unsorted);
+  int K = p.top_k[r];
+  if (K <= 0 || K > n_cand) K = n_cand;
+  const uint64_t* top = cand;
+  if (unsorted) {
+    sort_candidates(cand, n_cand);
+  } else if (n_cand > kpb && n_cand / kpb <= 32 && K <= 256) {
+    // few sorted blocks, small K: one warp holds a block's head per lane and takes the least composite K
+    // times (composites are distinct, so exactly one lane advances per step)
+    if (warp_id() == 0) {
+      const int lane = lane_id(), blocks = n_cand / kpb;
+      const uint64_t* mine = cand + (lane < blocks ? lane : 0) * kpb;
+      int pos = 0;
+      uint64_t cur = lane < blocks ? mine[0] : ~0ull;
+      for (int j = 0; j < K; ++j) {
+        uint64_t m = cur;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const uint64_t other = shfl_xor_u64(m, o);
+          m = other < m ? other : m;
+        }
+        if (lane == 0) merged[j] = m;
+        if (cur == m) {
+          ++pos;
+          cur = pos < kpb ? mine[pos] : ~0ull;
+        }
+      }
+    }
+    __syncthreads();
+    top = merged;
+  } else if (n_cand > kpb) {
+    const int blocks = n_cand / kpb;
+    for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
+      const int b = i / kpb;
+      int place = i - b * kpb;
+      if (place >= K) continue;
+      const uint64_t c = cand[i];
+      for (int o = 0; o < blocks && place < K; ++o)
+        if (o != b) place += count_below(cand + o * kpb, kpb, c);
+      if (place < K) merged[place] = c;
+    }
+    __syncthreads();
+    top = merged;
+  }
+  const float T_ = p.temperature[r];
+  int tok;
+  if (T_ < kSamplingEps) {
+    tok = id[at(cand_low(top[0]))];
+  } else {
+    tok = sample_tail<2>(
+        K, p.top_p[r], T_, s, [&](int i) { return key_f32(cand_key(top[i])); },
+        [&](int i) { return (int)id[at(cand_low(top[i]))]; }, [&](int i) { return un[at(cand_low(top[i]))]; });
+  }
+  if (threadIdx.x == 0) {
+    p.out[r] = tok;
+    if (xh) {
+      // the row is consumed: clear its arrival word; the last row's CTA of the step advances the step
+      *reinterpret_cast<volatile uint32_t*>(flag) = 0u;
+      __threadfence();
+      if (atomicAdd(&xh->done, 1u) == gridDim.x - 1) {
+        *reinterpret_cast<volatile uint32_t*>(&xh->done) = 0u;
+        __threadfence();
+        atomicAdd(&xh->step, 1u);
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------
@@ -2423,6 +2559,22 @@ int tlx_gumbel_argmax_dev(void* stream, const float* logits, const int32_t* idx0
   return gumbel_argmax_impl(stream, logits, idx0, idx1, rows, cols, 0u, 0u, key_dev, dim1_size, axis, out_pos);
 }
 
+static int launch_merge(cudaStream_t st, const MergeParams& p, int64_t rows) {
+  int P = 2;
+  while (P < p.n_cand) P <<= 1;
+  const size_t smem = kSharedHeader + (size_t)P * 8 + (size_t)p.n_cand * 8;
+  int rc;
+  if ((rc = ensure_smem((const void*)merge_and_sample_kernel, smem, "merge_and_sample")) != TLX_OK) return rc;
+  // one thread per two (padded) candidates: the sort's stages pair them up, the tail takes two items per thread
+  int threads = P / 2;
+  threads = threads < 64 ? 64 : (threads > kMergeThreads ? kMergeThreads : threads);
+  // many rows of few candidates: CTAs of 128 threads, eight per SM, so that a thousand rows are one wave
+  if (rows >= 256 && P <= 1024 && threads > 128) threads = 128;
+  merge_and_sample_kernel<<<(unsigned)rows, threads, smem, st>>>(p);
+  TLX_CHECK_LAUNCH("merge_and_sample");
+  return TLX_OK;
+}
+
 int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* cand_idx, const float* cand_noise,
                          int64_t rows, int n_cand, int k_per_block, int64_t block_stride, int64_t row_stride,
                          const int32_t* top_k, const float* top_p, const float* temperature, int32_t* out_tokens) {
@@ -2435,18 +2587,29 @@ int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* ca
   if (rows == 0) return TLX_OK;
   TLX_CHECK_ARG(cand_vals && cand_idx && cand_noise && top_k && top_p && temperature && out_tokens,
                 "merge_and_sample: null pointer");
-  int P = 2;
-  while (P < n_cand) P <<= 1;
-  const size_t smem = kSharedHeader + (size_t)P * 8;
-  int rc;
-  if ((rc = ensure_smem((const void*)merge_and_sample_kernel, smem, "merge_and_sample")) != TLX_OK) return rc;
-  // one thread per two (padded) candidates: the sort's stages pair them up, the tail takes two items per thread
-  int threads = P / 2;
-  threads = threads < 64 ? 64 : (threads > kMergeThreads ? kMergeThreads : threads);
-  merge_and_sample_kernel<<<(unsigned)rows, threads, smem, st>>>(
-      cand_vals, cand_idx, cand_noise, n_cand, k_per_block, block_stride, row_stride, top_k, top_p, temperature, out_tokens);
-  TLX_CHECK_LAUNCH("merge_and_sample");
-  return TLX_OK;
+  MergeParams p{};
+  p.cand_vals = cand_vals; p.cand_idx = cand_idx; p.cand_noise = cand_noise; p.n_cand = n_cand;
+  p.k_per_block = k_per_block; p.block_stride = block_stride; p.row_stride = row_stride; p.top_k = top_k;
+  p.top_p = top_p; p.temperature = temperature; p.out = out_tokens;
+  return launch_merge(st, p, rows);
+}
+
+int tlx_exchange_merge_and_sample(void* stream, void* exchange, int64_t rows, int k_cand, int world,
+                                  const int32_t* top_k, const float* top_p, const float* temperature,
+                                  int32_t* out_tokens, int32_t* out_status) {
+  cudaStream_t st = (cudaStream_t)stream;
+  TLX_CHECK_ARG(rows >= 1 && k_cand >= 1 && world >= 1 && world <= kExchangeMaxWorld, "exchange_merge_and_sample: bad extent");
+  if ((int64_t)world * k_cand > kMergeMaxCand)
+    return set_error(TLX_ERR_UNSUPPORTED, "exchange_merge_and_sample: %lld candidates exceed %d",
+                     (long long)world * k_cand, kMergeMaxCand);
+  TLX_CHECK_ARG(exchange && top_k && top_p && temperature && out_tokens, "exchange_merge_and_sample: null pointer");
+  const ExchangeLayout l = exchange_layout(rows, k_cand, world);
+  MergeParams p{};
+  p.n_cand = world * k_cand; p.k_per_block = k_cand; p.block_stride = (int64_t)l.block_elems; p.row_stride = k_cand;
+  p.top_k = top_k; p.top_p = top_p; p.temperature = temperature; p.out = out_tokens;
+  p.xbuf = (unsigned char*)exchange; p.world = world; p.rows = rows; p.status = out_status;
+  for (int q = 0; q < 2; ++q) { p.off_flags[q] = l.off_flags[q]; p.off_cand[q] = l.off_cand[q]; }
+  return launch_merge(st, p, rows);
 }
 
 }  // extern "C"

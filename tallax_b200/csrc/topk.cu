@@ -2,7 +2,10 @@
 // vocab-sharded sampler.  One CTA per row: the streaming collector leaves a superset of
 // the top-k in shared memory, a bitonic network orders it by (value desc, index asc).
 #include "select.cuh"
+#include "exchange.cuh"
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace tlx {
@@ -29,6 +32,7 @@ struct TopkParams {
   int64_t col_offset;
   int64_t dim0_offset;
   NoiseSrc noise;
+  ExchangeTargets ex;   // ex.world > 0: the candidates go to every rank's exchange buffer instead
 };
 
 template <int DT>
@@ -38,6 +42,67 @@ __device__ __forceinline__ typename Elem<DT>::type cast_replace(double v) {
   else if constexpr (DT == TLX_F16) return __float2half_rn((float)v);
   else if constexpr (DT == TLX_I32) return (int32_t)v;
   else return (uint32_t)v;
+}
+
+// Writes a row's results from its sorted candidate list (m valid entries, the first K are the answer).
+template <int DT>
+__device__ __forceinline__ void emit_row(const TopkParams& p, int64_t r, const typename Elem<DT>::type* __restrict__ row,
+                                         const uint64_t* cand, int m, const SelectShared& s) {
+  using T = typename Elem<DT>::type;
+  const int K = p.k_max;
+  const int k_row = p.k_per_row ? p.k_per_row[r] : K;
+  uint32_t par = 0;   // which of the exchange buffer's two sets this step uses
+  if (p.ex.world > 0) par = reinterpret_cast<volatile const ExchangeHeader*>(p.ex.peer[p.ex.rank])->step & 1u;
+  for (int j = threadIdx.x; j < K; j += blockDim.x) {
+    const uint64_t c = cand[j];
+    const int32_t col = (int32_t)cand_low(c);
+    const bool have = j < m;
+    if (p.cand_vals || p.ex.world > 0) {
+      // candidate stage: f32 value, global token id, noise at that token
+      const float v = have ? elem_as_float<DT>(row[col]) : -INFINITY;
+      const int64_t tok = (int64_t)col + p.col_offset;
+      float u = 0.5f;
+      if (have) u = p.noise.dense ? __ldg(p.noise.dense + r * p.noise.stride + col) : p.noise.at(r + p.dim0_offset, tok);
+      if (p.ex.world > 0) {
+        // slot `rank` of every rank's buffer, this rank's own included, starting with the next rank
+        const size_t plane = (size_t)p.rows * K;
+        for (int i = 0; i < p.ex.world; ++i) {
+          int peer = p.ex.rank + 1 + i;
+          if (peer >= p.ex.world) peer -= p.ex.world;
+          float* blk = reinterpret_cast<float*>(p.ex.peer[peer] + p.ex.off_cand[par]) + (size_t)p.ex.rank * 3 * plane;
+          blk[r * K + j] = v;
+          reinterpret_cast<int32_t*>(blk)[plane + r * K + j] = have ? (int32_t)tok : -1;
+          blk[2 * plane + r * K + j] = u;
+        }
+      } else {
+        p.cand_vals[r * K + j] = v;
+        p.cand_idx[r * K + j] = have ? (int32_t)tok : -1;
+        p.cand_noise[r * K + j] = u;
+      }
+    } else {
+      T v = have ? row[col] : cast_replace<DT>(0.0);
+      if (p.use_replace && j >= k_row) v = cast_replace<DT>(p.replace_val);
+      reinterpret_cast<T*>(p.out_vals)[r * K + j] = v;
+      p.out_idx[r * K + j] = have ? col : 0;
+    }
+  }
+  if (p.ex.world > 0) {
+    // the row's block is on its way to every rank: one arrival count each, released after the stores
+    __syncthreads();
+    if ((int)threadIdx.x < p.ex.world) {
+      __threadfence_system();
+      atomicAdd_system(reinterpret_cast<uint32_t*>(p.ex.peer[threadIdx.x] + p.ex.off_flags[par]) + r, 1u);
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (p.out_depths) p.out_depths[r] = s.refinements;
+    if (p.out_cutoff) {
+      if constexpr (DT == TLX_I32 || DT == TLX_U32)
+        reinterpret_cast<int32_t*>(p.out_cutoff)[r] = (int32_t)Elem<TLX_I32>::from_key((uint32_t)s.bin << kHistShift);
+      else
+        reinterpret_cast<float*>(p.out_cutoff)[r] = bin_lower_value(s.bin);
+    }
+  }
 }
 
 template <int DT, int CAP>
@@ -62,36 +127,285 @@ __global__ void __launch_bounds__(kTopkThreads) topk_kernel(TopkParams p) {
   const int m = min(s.fill, CAP);
   sort_candidates(cand, m);
 
-  const int k_row = p.k_per_row ? p.k_per_row[r] : K;
-  for (int j = threadIdx.x; j < K; j += blockDim.x) {
-    const uint64_t c = cand[j];
-    const int32_t col = (int32_t)cand_low(c);
-    const bool have = j < m;
-    if (p.cand_vals) {
-      // candidate stage: f32 value, global token id, noise at that token
-      const float v = have ? elem_as_float<DT>(row[col]) : -INFINITY;
-      const int64_t tok = (int64_t)col + p.col_offset;
-      p.cand_vals[r * K + j] = v;
-      p.cand_idx[r * K + j] = have ? (int32_t)tok : -1;
-      float u = 0.5f;
-      if (have) u = p.noise.dense ? __ldg(p.noise.dense + r * p.noise.stride + col) : p.noise.at(r + p.dim0_offset, tok);
-      p.cand_noise[r * K + j] = u;
-    } else {
-      T v = have ? row[col] : cast_replace<DT>(0.0);
-      if (p.use_replace && j >= k_row) v = cast_replace<DT>(p.replace_val);
-      reinterpret_cast<T*>(p.out_vals)[r * K + j] = v;
-      p.out_idx[r * K + j] = have ? col : 0;
+  emit_row<DT>(p, r, row, cand, m, s);
+}
+
+// ---- many short rows ---------------------------------------------------------------------------------
+// A CTA of 128 threads per row, eight of them per SM, two passes over the row (the second one finds the
+// row in L2).  Pass 1 keeps, per thread, the running maximum of every slot of its 16-byte vectors: 128 x
+// kSlots group maxima, each an element of the row.  The K-th largest of them (K <= number of groups) is
+// a lower bound of the row's K-th largest element, and with groups of a few dozen elements it is a tight
+// one: for K = 50 of 19 000 elements about K + 1 elements lie at or above it.  Pass 2 collects those, a
+// bitonic network orders them.  The bound is taken on the top 16 key bits.  NaNs have the greatest key:
+// the maxima skip them (so they stay elements of the row), pass 2 admits them by its negated compare.
+constexpr int kShortThreads = 128;
+constexpr int kShortCap = 1024;
+constexpr int kShortMaxK = 128;
+
+template <int DT> struct GroupMax;
+template <> struct GroupMax<TLX_BF16> {
+  static constexpr int kSlots = 8;
+  __nv_bfloat162 m[4];
+  __device__ __forceinline__ void init() {
+    const __nv_bfloat16 ninf = __float2bfloat16_rn(-INFINITY);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m[j] = __halves2bfloat162(ninf, ninf);
+  }
+  __device__ __forceinline__ void add(const uint4& v) {
+    const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m[j] = __hmax2(m[j], e[j]);
+  }
+  __device__ __forceinline__ void add_one(__nv_bfloat16 x) { m[0] = __hmax2(m[0], __halves2bfloat162(x, m[0].y)); }
+  __device__ __forceinline__ float slot(int j) const {
+    return (j & 1) ? __high2float(m[j >> 1]) : __low2float(m[j >> 1]);
+  }
+};
+template <> struct GroupMax<TLX_F16> {
+  static constexpr int kSlots = 8;
+  __half2 m[4];
+  __device__ __forceinline__ void init() {
+    const __half ninf = __float2half_rn(-INFINITY);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m[j] = __halves2half2(ninf, ninf);
+  }
+  __device__ __forceinline__ void add(const uint4& v) {
+    const __half2* e = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m[j] = __hmax2(m[j], e[j]);
+  }
+  __device__ __forceinline__ void add_one(__half x) { m[0] = __hmax2(m[0], __halves2half2(x, __high2half(m[0]))); }
+  __device__ __forceinline__ float slot(int j) const {
+    return (j & 1) ? __high2float(m[j >> 1]) : __low2float(m[j >> 1]);
+  }
+};
+template <> struct GroupMax<TLX_F32> {
+  static constexpr int kSlots = 4;
+  float m[4];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m[j] = -INFINITY;
+  }
+  __device__ __forceinline__ void add(const uint4& v) {
+    const float* e = reinterpret_cast<const float*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m[j] = fmaxf(m[j], e[j]);
+  }
+  __device__ __forceinline__ void add_one(float x) { m[0] = fmaxf(m[0], x); }
+  __device__ __forceinline__ float slot(int j) const { return m[j]; }
+};
+
+// Row traversal by 16-byte vectors: fv(vector, first column) in the aligned body, kU loads in flight per
+// thread; fs(element, column) for the unaligned head and tail.  sub > 1 visits only every sub-th run of
+// blockDim vectors (a sample of the row in contiguous 2 KB pieces).
+template <int DT, int kU, typename FV, typename FS>
+__device__ __forceinline__ void for_each_vec(const typename Elem<DT>::type* __restrict__ row, int64_t n, int sub, FV&& fv,
+                                             FS&& fs) {
+  using T = typename Elem<DT>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(row);
+  int64_t head = (int64_t)(((16 - (addr & 15)) & 15) / sizeof(T));
+  if (head > n) head = n;
+  for (int64_t c = threadIdx.x; c < head; c += blockDim.x) fs(row[c], c);
+  const int64_t nvec = (n - head) / VEC;
+  const uint4* vp = reinterpret_cast<const uint4*>(row + head);
+  const int64_t step = (int64_t)blockDim.x * sub;
+  int64_t i = threadIdx.x;
+  for (; i + (int64_t)(kU - 1) * step < nvec; i += (int64_t)kU * step) {
+    uint4 v[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) v[u] = __ldg(vp + i + (int64_t)u * step);
+#pragma unroll
+    for (int u = 0; u < kU; ++u) fv(v[u], head + (i + (int64_t)u * step) * VEC);
+  }
+#pragma unroll 1
+  for (; i < nvec; i += step) fv(__ldg(vp + i), head + i * VEC);
+#pragma unroll 1
+  for (int64_t c = head + nvec * VEC + threadIdx.x; c < n; c += blockDim.x) fs(row[c], c);
+}
+
+// Out of line on purpose: the few vectors of a row that hold an element at or above the bound come here,
+// so that the streaming loop around the call stays small.
+template <int DT>
+static __device__ __noinline__ void push_vector(uint4 v, int64_t cb, uint32_t t16, float thr, int* fill, uint64_t* cand,
+                                            int cap) {
+  using T = typename Elem<DT>::type;
+  const T* x = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int j = 0; j < 16 / (int)sizeof(T); ++j) {
+    if (!(elem_as_float<DT>(x[j]) < thr)) {
+      const uint32_t key = Elem<DT>::key(x[j]);
+      if ((key >> 16) >= t16) {
+        const int slot = atomicAdd(fill, 1);
+        if (slot < cap) cand[slot] = cand_make(key, (uint32_t)(cb + j));
+      }
     }
   }
-  if (threadIdx.x == 0) {
-    if (p.out_depths) p.out_depths[r] = s.refinements;
-    if (p.out_cutoff) {
-      if constexpr (DT == TLX_I32 || DT == TLX_U32)
-        reinterpret_cast<int32_t*>(p.out_cutoff)[r] = (int32_t)Elem<TLX_I32>::from_key((uint32_t)s.bin << kHistShift);
-      else
-        reinterpret_cast<float*>(p.out_cutoff)[r] = bin_lower_value(s.bin);
+}
+
+// The K-th largest of the G 16-bit keys in shared memory (1 <= K <= G): two counting passes of 8 bits.
+// hist: 256 words, scan: 40 words, pick: 2 words, all in shared memory.  All threads call; blockDim
+// divides 256.
+static __device__ __noinline__ uint32_t kth_largest_u16(const uint16_t* keys, int G, int K, uint32_t* hist,
+                                                    uint32_t* scan, int* pick) {
+  const int per = 256 / blockDim.x;
+  uint32_t prefix = 0;
+  int need = K;
+  for (int pass = 0; pass < 2; ++pass) {
+    const int sh = pass ? 0 : 8;
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < G; i += blockDim.x) {
+      const uint32_t k = keys[i];
+      if (pass == 0 || (k >> 8) == prefix) atomicAdd(&hist[(k >> sh) & 255u], 1u);
+    }
+    __syncthreads();
+    const int hi = 255 - threadIdx.x * per;   // thread t owns bins hi, hi-1, ... (descending)
+    uint32_t local = 0;
+    for (int j = 0; j < per; ++j) local += hist[hi - j];
+    uint32_t total;
+    const uint32_t incl = block_scan_incl<uint32_t>(local, scan, &total, ShflUpU32());
+    const uint32_t excl = incl - local;
+    if (excl < (uint32_t)need && incl >= (uint32_t)need) {
+      uint32_t run = excl;
+      for (int j = 0; j < per; ++j) {
+        const uint32_t c = hist[hi - j];
+        if (run + c >= (uint32_t)need) { pick[0] = hi - j; pick[1] = (int)run; break; }
+        run += c;
+      }
+    }
+    __syncthreads();
+    const int b = pick[0], above = pick[1];
+    __syncthreads();
+    prefix = pass ? ((prefix << 8) | (uint32_t)b) : (uint32_t)b;
+    need -= above;
+  }
+  return prefix;
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams p) {
+  using T = typename Elem<DT>::type;
+  constexpr int kSlots = GroupMax<DT>::kSlots;
+  constexpr int G = kShortThreads * kSlots;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  SelectShared& s = *reinterpret_cast<SelectShared*>(smem_raw);
+  uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
+  // the group keys and the small histogram live in the big histogram's space, which only the fallback uses
+  uint16_t* gkeys = reinterpret_cast<uint16_t*>(s.hist);            // G * 2 bytes <= 2 KB
+  uint32_t* hist8 = s.hist + 1024;                                    // 256 words
+  const int64_t r = blockIdx.x;
+  const T* row = reinterpret_cast<const T*>(p.x) + r * p.row_stride;
+  const int K = p.k_max;
+  const int64_t n = p.n;
+
+  // rows that L2 would not keep between the passes give their bound from a quarter of the row
+  const int sub = n * (int64_t)sizeof(T) > (128 << 10) ? 4 : 1;
+  GroupMax<DT> gm;
+  gm.init();
+  for_each_vec<DT, 8>(row, n, sub, [&](const uint4& v, int64_t) { gm.add(v); }, [&](T x, int64_t) { gm.add_one(x); });
+#pragma unroll
+  for (int j = 0; j < kSlots; ++j) gkeys[threadIdx.x * kSlots + j] = (uint16_t)(f32_key(gm.slot(j)) >> 16);
+  if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
+  __syncthreads();
+  const uint32_t t16 = kth_largest_u16(gkeys, G, K, hist8, s.scan_u32, s.tmp_i);
+  // lower edge of the bound's 16-bit bin as a value; a NaN pattern (the bin of -inf) admits everything
+  const float thr = key_f32(t16 << 16);
+
+  auto push_one = [&](T x, int64_t c) {
+    if (!(elem_as_float<DT>(x) < thr)) {
+      const uint32_t key = Elem<DT>::key(x);
+      if ((key >> 16) >= t16) {
+        const int slot = atomicAdd(&s.fill, 1);
+        if (slot < kShortCap) cand[slot] = cand_make(key, (uint32_t)c);
+      }
+    }
+  };
+  if constexpr (DT == TLX_BF16) {
+    const __nv_bfloat16 tb = __ushort_as_bfloat16((unsigned short)(__float_as_uint(thr) >> 16));
+    const __nv_bfloat162 t2 = __halves2bfloat162(tb, tb);
+    for_each_vec<DT, 8>(row, n, 1,
+      [&](const uint4& v, int64_t cb) {
+        const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
+        // __hblt2: both halves less than the bound (false when either is a NaN)
+        if (!(__hblt2(e[0], t2) && __hblt2(e[1], t2) && __hblt2(e[2], t2) && __hblt2(e[3], t2)))
+          push_vector<DT>(v, cb, t16, thr, &s.fill, cand, kShortCap);
+      },
+      push_one);
+  } else if constexpr (DT == TLX_F16) {
+    for_each_vec<DT, 8>(row, n, 1,
+      [&](const uint4& v, int64_t cb) {
+        const __half2* e = reinterpret_cast<const __half2*>(&v);
+        bool any = false;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(e[j]);
+          any = any || !(f.x < thr) || !(f.y < thr);
+        }
+        if (any) push_vector<DT>(v, cb, t16, thr, &s.fill, cand, kShortCap);
+      },
+      push_one);
+  } else {
+    for_each_vec<DT, 8>(row, n, 1,
+      [&](const uint4& v, int64_t cb) {
+        const float* e = reinterpret_cast<const float*>(&v);
+        if (!(e[0] < thr) || !(e[1] < thr) || !(e[2] < thr) || !(e[3] < thr))
+          push_vector<DT>(v, cb, t16, thr, &s.fill, cand, kShortCap);
+      },
+      push_one);
+  }
+  __syncthreads();
+  if (s.fill > kShortCap) exact_select_row<DT>(row, n, K, s, cand);   // huge groups of equal values
+  const int m = min(s.fill, kShortCap);
+  if (m <= 96) {
+    // a handful of candidates: every thread counts the composites below its own (they are distinct) and
+    // puts it at that place; no network, no barriers in between
+    uint64_t* placed = reinterpret_cast<uint64_t*>(s.hist + 2048);   // 96 slots in the fallback's histogram space
+    if ((int)threadIdx.x < m) {
+      const uint64_t c = cand[threadIdx.x];
+      int below = 0;
+      for (int i = 0; i < m; ++i) below += cand[i] < c ? 1 : 0;
+      placed[below] = c;
+    }
+    __syncthreads();
+    emit_row<DT>(p, r, row, placed, m, s);
+  } else {
+    sort_candidates(cand, m);
+    emit_row<DT>(p, r, row, cand, m, s);
+  }
+}
+
+// Whether the two-pass kernel serves a call: floating-point rows, K <= 128, exact mode without the
+// diagnostics of the one-pass kernel, and enough rows to fill the eight CTAs per SM.
+static bool short_rows_apply(int dtype, const TopkParams& p) {
+  static const char* force = getenv("TLX_TOPK_PATH");   // "short" / "long": comparison runs
+  if (dtype != TLX_F32 && dtype != TLX_BF16 && dtype != TLX_F16) return false;
+  if (p.k_max > kShortMaxK || p.mode != 0 || p.out_valid || p.out_depths || p.out_cutoff) return false;
+  if (force && !strcmp(force, "short")) return true;
+  if (force && !strcmp(force, "long")) return false;
+  return p.rows >= 256 && p.n >= 2048;
+}
+
+template <int DT>
+static int launch_topk_short(cudaStream_t st, const TopkParams& p) {
+  const size_t smem = ((sizeof(SelectShared) + 15) & ~size_t(15)) + (size_t)kShortCap * 8;
+  // eight CTAs of 25 KB per SM need the large shared-memory configuration: asked for once per device
+  static std::mutex mu;
+  static bool asked[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !asked[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(topk_short_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           (int)cudaSharedmemCarveoutMaxShared);
+      if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "top_k: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      if (dev >= 0 && dev < 64) asked[dev] = true;
     }
   }
+  topk_short_kernel<DT><<<(unsigned)p.rows, kShortThreads, smem, st>>>(p);
+  TLX_CHECK_LAUNCH("top_k (short rows)");
+  return TLX_OK;
 }
 
 template <int DT, int CAP>
@@ -129,6 +443,13 @@ static int launch_topk(cudaStream_t st, const TopkParams& p) {
 }
 
 static int dispatch_topk(cudaStream_t st, int dtype, const TopkParams& p, const char* what) {
+  if (short_rows_apply(dtype, p)) {
+    switch (dtype) {
+      case TLX_F32: return launch_topk_short<TLX_F32>(st, p);
+      case TLX_BF16: return launch_topk_short<TLX_BF16>(st, p);
+      default: return launch_topk_short<TLX_F16>(st, p);
+    }
+  }
   switch (dtype) {
     case TLX_F32: return launch_topk<TLX_F32>(st, p);
     case TLX_BF16: return launch_topk<TLX_BF16>(st, p);
@@ -239,7 +560,8 @@ static int shard_candidates_impl(void* stream, const void* logits, int dtype, in
                                  int64_t row_stride, int64_t col_offset, int k_cand, const float* noise,
                                  int64_t noise_stride, uint32_t key0, uint32_t key1, const uint32_t* key_dev,
                                  int64_t vocab_total, int64_t dim0_offset, const int32_t* dim0_offset_dev,
-                                 float* out_vals, int32_t* out_idx, float* out_noise) {
+                                 float* out_vals, int32_t* out_idx, float* out_noise,
+                                 const ExchangeTargets* ex = nullptr) {
   cudaStream_t st = (cudaStream_t)stream;
   TLX_CHECK_ARG(rows >= 0 && v_local > 0, "shard_candidates: bad extent");
   TLX_CHECK_ARG(k_cand >= 1 && k_cand <= 1024, "shard_candidates: k_cand must be in [1, 1024], got %d", k_cand);
@@ -248,8 +570,9 @@ static int shard_candidates_impl(void* stream, const void* logits, int dtype, in
   TLX_CHECK_ARG(row_stride >= v_local, "shard_candidates: row stride smaller than the row");
   TLX_CHECK_ARG(col_offset >= 0 && col_offset + v_local <= (1ll << 31), "shard_candidates: token ids exceed int32");
   if (rows == 0) return TLX_OK;
-  TLX_CHECK_ARG(logits && out_vals && out_idx && out_noise, "shard_candidates: null pointer");
+  TLX_CHECK_ARG(logits && (ex || (out_vals && out_idx && out_noise)), "shard_candidates: null pointer");
   TopkParams p{};
+  if (ex) p.ex = *ex;
   p.x = logits; p.rows = rows; p.n = v_local; p.row_stride = row_stride; p.k_max = k_cand;
   p.cand_vals = out_vals; p.cand_idx = out_idx; p.cand_noise = out_noise; p.col_offset = col_offset;
   p.dim0_offset = dim0_offset;
@@ -274,6 +597,28 @@ int tlx_shard_candidates_dev(void* stream, const void* logits, int dtype, int64_
   if (!noise && !key_dev) return set_error(TLX_ERR_INVALID, "shard_candidates: neither noise nor a key given");
   return shard_candidates_impl(stream, logits, dtype, rows, v_local, row_stride, col_offset, k_cand, noise, noise_stride,
                                0u, 0u, key_dev, vocab_total, 0, dim0_offset_dev, out_vals, out_idx, out_noise);
+}
+
+int tlx_exchange_shard_candidates(void* stream, const void* logits, int dtype, int64_t rows, int64_t v_local,
+                                  int64_t row_stride, int64_t col_offset, int k_cand, const float* noise,
+                                  int64_t noise_stride, const uint32_t* key_dev, uint32_t key0, uint32_t key1,
+                                  int64_t vocab_total, int64_t dim0_offset, const int32_t* dim0_offset_dev, int rank,
+                                  int world, void* const* exchange_of_rank) {
+  TLX_CHECK_ARG(world >= 1 && world <= kExchangeMaxWorld && rank >= 0 && rank < world,
+                "exchange_shard_candidates: rank %d of %d", rank, world);
+  TLX_CHECK_ARG(exchange_of_rank && rows >= 1 && k_cand >= 1, "exchange_shard_candidates: bad argument");
+  ExchangeTargets ex{};
+  ex.world = world;
+  ex.rank = rank;
+  const ExchangeLayout l = exchange_layout(rows, k_cand, world);
+  for (int q = 0; q < 2; ++q) { ex.off_flags[q] = l.off_flags[q]; ex.off_cand[q] = l.off_cand[q]; }
+  for (int i = 0; i < world; ++i) {
+    TLX_CHECK_ARG(exchange_of_rank[i], "exchange_shard_candidates: buffer of rank %d is null", i);
+    ex.peer[i] = (unsigned char*)exchange_of_rank[i];
+  }
+  return shard_candidates_impl(stream, logits, dtype, rows, v_local, row_stride, col_offset, k_cand, noise, noise_stride,
+                               key0, key1, key_dev, vocab_total, dim0_offset, dim0_offset_dev, nullptr, nullptr, nullptr,
+                               &ex);
 }
 
 }  // extern "C"

@@ -8,6 +8,8 @@ from tallax_b200._src.sampling import top_p_and_sample as top_p_and_sample
 from tallax_b200._src.sampling import sample as sample
 from tallax_b200._src.sampling import sample_vocab_sharded as sample_vocab_sharded
 from tallax_b200._src.sampling import VocabShardedWorkspace as VocabShardedWorkspace
+from tallax_b200._src.sampling import make_vocab_exchange as make_vocab_exchange
 from tallax_b200._src.sampling import SamplingMetadata as SamplingMetadata
 
-__all__ = ["top_p_mask", "top_p_and_sample", "sample", "sample_vocab_sharded", "VocabShardedWorkspace", "SamplingMetadata"]
+__all__ = ["top_p_mask", "top_p_and_sample", "sample", "sample_vocab_sharded", "VocabShardedWorkspace",
+           "make_vocab_exchange", "SamplingMetadata"]

@@ -1,4 +1,5 @@
-"""Two-GPU run of the vocab-sharded sampler over NCCL (skipped with fewer than two GPUs)."""
+"""Two-GPU run of the vocab-sharded sampler, over NCCL and over the peer-memory exchange (skipped with fewer
+than two GPUs)."""
 import datetime
 import os
 import queue
@@ -38,7 +39,19 @@ def _worker(rank, world, port, q):
         tok = sampling.sample_vocab_sharded(None, to_dev(x[:, rank * vl:(rank + 1) * vl], dev), md,
                                             noise_shard=to_dev(noise[:, rank * vl:(rank + 1) * vl], dev), k_cand=50)
         torch.cuda.synchronize()
-        q.put((rank, tok.cpu().numpy().tolist()))
+        # the same steps with the candidates exchanged by the kernels themselves: three steps (both sets of
+        # the exchange buffer and a reuse), each must give the tokens of the NCCL path
+        ex = sampling.make_vocab_exchange(B, 50, device=dev)
+        same = True
+        for _ in range(3):
+            tok2 = sampling.sample_vocab_sharded(None, to_dev(x[:, rank * vl:(rank + 1) * vl], dev), md,
+                                                 noise_shard=to_dev(noise[:, rank * vl:(rank + 1) * vl], dev),
+                                                 k_cand=50, exchange=ex)
+            same = same and bool((tok2 == tok).all())
+        steps, err = ex.state()
+        dist.barrier()          # no rank unmaps a buffer that another may still write
+        ex.close()
+        q.put((rank, tok.cpu().numpy().tolist(), same, steps, err))
     finally:
         dist.destroy_process_group()
 
@@ -59,7 +72,8 @@ def test_vocab_sharded_two_gpus(cuda):
         got = {}
         for _ in range(world):
             try:
-                rank, toks = q.get(timeout=300)
+                rank, toks, same, steps, err = q.get(timeout=300)
+                assert same and steps == 3 and err == 0, (rank, same, steps, err)
             except queue.Empty:
                 pytest.fail("a rank delivered no result: exit codes %r" % [p.exitcode for p in procs])
             got[rank] = toks

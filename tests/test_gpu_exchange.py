@@ -1,0 +1,98 @@
+"""The peer-memory candidate exchange of the vocab-sharded sampler on ONE GPU: the ranks are stood in for by
+successive launches on one stream (every rank's candidate kernel, then every rank's merge kernel), so that no
+kernel ever waits for one that has not run.  The two-GPU run is in test_gpu_distributed.py."""
+import numpy as np
+import pytest
+
+from oracle import tallax_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world,dtype,k", [(1, "bf16", 50), (2, "bf16", 50), (4, "f32", 64), (8, "bf16", 128)])
+def test_exchange_matches_the_gathered_path_and_the_oracle(cuda, world, dtype, k):
+    import torch
+    from tallax_b200 import sampling
+    from tallax_b200._src import ops
+    from tests.conftest import to_dev
+
+    dev = torch.device("cuda", 0)
+    B, V = 48, 4096 * world
+    group = ops.Exchange.local_group(B, k, world, dev)
+    try:
+        for step in range(3):
+            x, tk, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=10 + step, dtype=dtype)
+            tk = np.minimum(tk, k).astype(np.int32)
+            vl = V // world
+            xs = [to_dev(x[:, r * vl:(r + 1) * vl], dev).contiguous() for r in range(world)]
+            ns = [to_dev(noise[:, r * vl:(r + 1) * vl], dev).contiguous() for r in range(world)]
+            dtk, dtp, dT = to_dev(tk, dev), to_dev(tp, dev), to_dev(T, dev)
+            for r in range(world):
+                ops.exchange_shard_candidates(xs[r], r * vl, group[r], noise_shard=ns[r], vocab_total=V)
+            toks = [ops.exchange_merge_and_sample(group[r], dtk, dtp, dT).cpu().numpy() for r in range(world)]
+            # the gathered path on the same shards
+            gathered = torch.stack([ops.shard_candidates(xs[r], r * vl, k, noise_shard=ns[r], vocab_total=V)
+                                    for r in range(world)])
+            ref = ops.merge_and_sample(gathered, dtk, dtp, dT).cpu().numpy()
+            exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
+            for r in range(world):
+                assert (toks[r] == ref).all()
+                assert not ((toks[r] != exp) & ~flags).any()
+                assert group[r].state() == (step + 1, 0)
+    finally:
+        for e in group:
+            e.close()
+
+
+def test_exchange_with_key_noise(cuda):
+    import torch
+    from tallax_b200._src import ops
+    from tests.conftest import to_dev
+
+    dev = torch.device("cuda", 0)
+    world, B, V, k = 2, 16, 8192, 32
+    group = ops.Exchange.local_group(B, k, world, dev)
+    try:
+        x, tk, tp, T, _ = o.make_sharded_inputs(B=B, V=V, seed=3, dtype="bf16")
+        tk = np.minimum(tk, k).astype(np.int32)
+        vl = V // world
+        key = (7, 11)
+        xs = [to_dev(x[:, r * vl:(r + 1) * vl], dev).contiguous() for r in range(world)]
+        dtk, dtp, dT = to_dev(tk, dev), to_dev(tp, dev), to_dev(T, dev)
+        for r in range(world):
+            ops.exchange_shard_candidates(xs[r], r * vl, group[r], rng_key=key, vocab_total=V, dim0_offset=5)
+        tok = ops.exchange_merge_and_sample(group[0], dtk, dtp, dT).cpu().numpy()
+        ops.exchange_merge_and_sample(group[1], dtk, dtp, dT)
+        gathered = torch.stack([ops.shard_candidates(xs[r], r * vl, k, rng_key=key, vocab_total=V, dim0_offset=5)
+                                for r in range(world)])
+        ref = ops.merge_and_sample(gathered, dtk, dtp, dT).cpu().numpy()
+        assert (tok == ref).all()
+    finally:
+        for e in group:
+            e.close()
+
+
+def test_a_missing_rank_is_reported_not_waited_for_forever(cuda):
+    """Only rank 0 of two delivers: the merge kernel's bounded wait (two seconds) gives up, sets the status and
+    the buffer's error word, and the context stays usable."""
+    import torch
+    from tallax_b200._src import ops
+    from tests.conftest import to_dev
+
+    dev = torch.device("cuda", 0)
+    world, B, V, k = 2, 4, 4096, 16
+    group = ops.Exchange.local_group(B, k, world, dev)
+    try:
+        x, tk, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=1, dtype="bf16")
+        vl = V // world
+        ops.exchange_shard_candidates(to_dev(x[:, :vl], dev).contiguous(), 0, group[0],
+                                      noise_shard=to_dev(noise[:, :vl], dev).contiguous(), vocab_total=V)
+        ops.exchange_merge_and_sample(group[0], to_dev(np.minimum(tk, k).astype(np.int32), dev), to_dev(tp, dev),
+                                      to_dev(T, dev))
+        torch.cuda.synchronize()
+        assert int(group[0].status.item()) == 1
+        assert group[0].state()[1] == 1
+        assert float(torch.ones(4, device=dev).sum()) == 4.0       # the context still works
+    finally:
+        for e in group:
+            e.close()
