@@ -1803,9 +1803,9 @@ __device__ __forceinline__ int count_below(const uint64_t* blk, int len, uint64_
 }
 
 // One CTA per row.  The shards' blocks arrive sorted (value desc, token asc), which the kernel checks: a
-// few blocks and a small K are merged by one warp (a head per lane, the least of them K times); otherwise a
-// candidate's place in the merged order is its place in its own block plus, for every other block, the
-// number of entries that precede it there (a binary search), and only places below K are filled.
+// candidate's place in the merged order is then its place in its own block plus, for every other block,
+// the number of entries that precede it there (a binary search), and only places below K are filled; one
+// comparison per block rules most candidates out before any search.
 // Unsorted blocks take the bitonic network over all candidates instead.
 __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergeParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -1865,39 +1865,24 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
   const uint64_t* top = cand;
   if (unsorted) {
     sort_candidates(cand, n_cand);
-  } else if (n_cand > kpb && n_cand / kpb <= 32 && K <= 256) {
-    // few sorted blocks, small K: one warp holds a block's head per lane and takes the least composite K
-    // times (composites are distinct, so exactly one lane advances per step)
-    if (warp_id() == 0) {
-      const int lane = lane_id(), blocks = n_cand / kpb;
-      const uint64_t* mine = cand + (lane < blocks ? lane : 0) * kpb;
-      int pos = 0;
-      uint64_t cur = lane < blocks ? mine[0] : ~0ull;
-      for (int j = 0; j < K; ++j) {
-        uint64_t m = cur;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const uint64_t other = shfl_xor_u64(m, o);
-          m = other < m ? other : m;
-        }
-        if (lane == 0) merged[j] = m;
-        if (cur == m) {
-          ++pos;
-          cur = pos < kpb ? mine[pos] : ~0ull;
-        }
-      }
-    }
-    __syncthreads();
-    top = merged;
   } else if (n_cand > kpb) {
     const int blocks = n_cand / kpb;
     for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
       const int b = i / kpb;
-      int place = i - b * kpb;
-      if (place >= K) continue;
+      const int q = i - b * kpb;
+      if (q >= K) continue;
       const uint64_t c = cand[i];
+      // q entries of its own block precede the candidate: if entry K-1-q of another block does too, so do
+      // that block's K-q first entries, and the candidate's place is K or more
+      const int probe = K - 1 - q;
+      bool out = false;
+      if (probe < kpb)
+        for (int o = 0; o < blocks && !out; ++o) out = o != b && cand[o * kpb + probe] < c;
+      if (out) continue;
+      int place = q;
+      const int span = min(kpb, probe + 1);   // a block's entries from `span` on cannot change the verdict
       for (int o = 0; o < blocks && place < K; ++o)
-        if (o != b) place += count_below(cand + o * kpb, kpb, c);
+        if (o != b) place += count_below(cand + o * kpb, span, c);
       if (place < K) merged[place] = c;
     }
     __syncthreads();
@@ -2570,6 +2555,12 @@ static int launch_merge(cudaStream_t st, const MergeParams& p, int64_t rows) {
   threads = threads < 64 ? 64 : (threads > kMergeThreads ? kMergeThreads : threads);
   // many rows of few candidates: CTAs of 128 threads, eight per SM, so that a thousand rows are one wave
   if (rows >= 256 && P <= 1024 && threads > 128) threads = 128;
+  if (p.xbuf) {
+    // exchange mode: the rows' arrival counts order this kernel after the candidate kernels, so it may be
+    // scheduled while this rank's candidate kernel still runs (its CTAs have all started by then) and has
+    // its launch latency behind it when the first rows arrive
+    return launch_dependent(merge_and_sample_kernel, (unsigned)rows, (unsigned)threads, smem, st, "merge_and_sample", p);
+  }
   merge_and_sample_kernel<<<(unsigned)rows, threads, smem, st>>>(p);
   TLX_CHECK_LAUNCH("merge_and_sample");
   return TLX_OK;

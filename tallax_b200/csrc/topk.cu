@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(kTopkThreads) topk_kernel(TopkParams p) {
   const int64_t r = blockIdx.x;
   const T* row = reinterpret_cast<const T*>(p.x) + r * p.row_stride;
   const int K = p.k_max;
+  // exchange mode: the merge kernel that follows waits for the rows' arrival counts, not for this kernel
+  if (p.ex.world > 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   bool ok = collect_row<DT, CAP>(row, p.n, K, s, cand);
   if (!ok) {
@@ -298,6 +300,8 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
   const T* row = reinterpret_cast<const T*>(p.x) + r * p.row_stride;
   const int K = p.k_max;
   const int64_t n = p.n;
+  // exchange mode: the merge kernel that follows waits for the rows' arrival counts, not for this kernel
+  if (p.ex.world > 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // rows that L2 would not keep between the passes give their bound from a quarter of the row
   const int sub = n * (int64_t)sizeof(T) > (128 << 10) ? 4 : 1;
