@@ -1866,21 +1866,33 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
   if (unsorted) {
     sort_candidates(cand, n_cand);
   } else if (n_cand > kpb) {
+    // Step 1, every candidate: q entries of its own block precede it; if entry K-1-q of another block does
+    // too, so do that block's first K-q entries and its place is K or more.  The others (K and a few more
+    // per block) are listed.  Step 2, one listed candidate per thread: a binary search per other block.
     const int blocks = n_cand / kpb;
+    uint32_t* listed = reinterpret_cast<uint32_t*>(merged + n_cand);
+    if (threadIdx.x == 0) s.fill = 0;
+    __syncthreads();
     for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
       const int b = i / kpb;
       const int q = i - b * kpb;
       if (q >= K) continue;
       const uint64_t c = cand[i];
-      // q entries of its own block precede the candidate: if entry K-1-q of another block does too, so do
-      // that block's K-q first entries, and the candidate's place is K or more
       const int probe = K - 1 - q;
       bool out = false;
       if (probe < kpb)
         for (int o = 0; o < blocks && !out; ++o) out = o != b && cand[o * kpb + probe] < c;
-      if (out) continue;
+      if (!out) listed[atomicAdd(&s.fill, 1)] = (uint32_t)i;
+    }
+    __syncthreads();
+    const int nlisted = s.fill;
+    for (int l = threadIdx.x; l < nlisted; l += blockDim.x) {
+      const int i = (int)listed[l];
+      const int b = i / kpb;
+      const int q = i - b * kpb;
+      const uint64_t c = cand[i];
       int place = q;
-      const int span = min(kpb, probe + 1);   // a block's entries from `span` on cannot change the verdict
+      const int span = min(kpb, K - q);   // a block's entries from `span` on cannot change the verdict
       for (int o = 0; o < blocks && place < K; ++o)
         if (o != b) place += count_below(cand + o * kpb, span, c);
       if (place < K) merged[place] = c;
@@ -2547,7 +2559,7 @@ int tlx_gumbel_argmax_dev(void* stream, const float* logits, const int32_t* idx0
 static int launch_merge(cudaStream_t st, const MergeParams& p, int64_t rows) {
   int P = 2;
   while (P < p.n_cand) P <<= 1;
-  const size_t smem = kSharedHeader + (size_t)P * 8 + (size_t)p.n_cand * 8;
+  const size_t smem = kSharedHeader + (size_t)P * 8 + (size_t)p.n_cand * 12;   // candidates, merged order, list
   int rc;
   if ((rc = ensure_smem((const void*)merge_and_sample_kernel, smem, "merge_and_sample")) != TLX_OK) return rc;
   // one thread per two (padded) candidates: the sort's stages pair them up, the tail takes two items per thread

@@ -226,8 +226,7 @@ __device__ __forceinline__ void for_each_vec(const typename Elem<DT>::type* __re
   for (int64_t c = head + nvec * VEC + threadIdx.x; c < n; c += blockDim.x) fs(row[c], c);
 }
 
-// Out of line on purpose: the few vectors of a row that hold an element at or above the bound come here,
-// so that the streaming loop around the call stays small.
+// The elements of one vector that lie at or above the bound join the candidate list.
 template <int DT>
 static __device__ __noinline__ void push_vector(uint4 v, int64_t cb, uint32_t t16, float thr, int* fill, uint64_t* cand,
                                             int cap) {
@@ -325,6 +324,16 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
       }
     }
   };
+  // The streaming loop only notes which vectors hold an element at or above the bound (about one per
+  // candidate); the noted vectors are then read again, one per thread, and their elements pushed.
+  uint32_t* noted = s.hist + 2048;          // up to kShortCap first columns, in the fallback's histogram space
+  int* nnoted = &s.tmp_i[2];
+  if (threadIdx.x == 0) *nnoted = 0;
+  __syncthreads();
+  auto note = [&](int64_t cb) {
+    const int slot = atomicAdd(nnoted, 1);
+    if (slot < kShortCap) noted[slot] = (uint32_t)cb;
+  };
   if constexpr (DT == TLX_BF16) {
     const __nv_bfloat16 tb = __ushort_as_bfloat16((unsigned short)(__float_as_uint(thr) >> 16));
     const __nv_bfloat162 t2 = __halves2bfloat162(tb, tb);
@@ -332,8 +341,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
       [&](const uint4& v, int64_t cb) {
         const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
         // __hblt2: both halves less than the bound (false when either is a NaN)
-        if (!(__hblt2(e[0], t2) && __hblt2(e[1], t2) && __hblt2(e[2], t2) && __hblt2(e[3], t2)))
-          push_vector<DT>(v, cb, t16, thr, &s.fill, cand, kShortCap);
+        if (!(__hblt2(e[0], t2) && __hblt2(e[1], t2) && __hblt2(e[2], t2) && __hblt2(e[3], t2))) note(cb);
       },
       push_one);
   } else if constexpr (DT == TLX_F16) {
@@ -346,17 +354,25 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
           const float2 f = __half22float2(e[j]);
           any = any || !(f.x < thr) || !(f.y < thr);
         }
-        if (any) push_vector<DT>(v, cb, t16, thr, &s.fill, cand, kShortCap);
+        if (any) note(cb);
       },
       push_one);
   } else {
     for_each_vec<DT, 8>(row, n, 1,
       [&](const uint4& v, int64_t cb) {
         const float* e = reinterpret_cast<const float*>(&v);
-        if (!(e[0] < thr) || !(e[1] < thr) || !(e[2] < thr) || !(e[3] < thr))
-          push_vector<DT>(v, cb, t16, thr, &s.fill, cand, kShortCap);
+        if (!(e[0] < thr) || !(e[1] < thr) || !(e[2] < thr) || !(e[3] < thr)) note(cb);
       },
       push_one);
+  }
+  __syncthreads();
+  if (*nnoted > kShortCap) {
+    if (threadIdx.x == 0) s.fill = kShortCap + 1;   // more vectors than the list holds: the exact fallback
+  } else {
+    for (int l = threadIdx.x; l < *nnoted; l += blockDim.x) {
+      const int64_t cb = noted[l];
+      push_vector<DT>(__ldg(reinterpret_cast<const uint4*>(row + cb)), cb, t16, thr, &s.fill, cand, kShortCap);
+    }
   }
   __syncthreads();
   if (s.fill > kShortCap) exact_select_row<DT>(row, n, K, s, cand);   // huge groups of equal values
