@@ -111,7 +111,67 @@ ffi::Error ShardCandidatesImpl(cudaStream_t stream, ffi::AnyBuffer logits, ffi::
                                            reinterpret_cast<int32_t*>(base + plane), base + 2 * plane, nullptr, 0));
 }
 
+// The vocab-sharded sampler with the all_gather of tallax/_src/sampling.py:312-316 done by the kernels over
+// peer memory: the exchange buffers are made and mapped at set-up (tlx_exchange_create / tlx_exchange_open on
+// the host, outside jit); their device addresses reach the handlers as attributes, `exchange_of_rank` holding
+// the `world` addresses in rank order.  Stage 1 has no result of its own (a dummy token keeps XLA's ordering:
+// stage 2 takes it as an operand).
+ffi::Error ExchangeShardCandidatesImpl(cudaStream_t stream, ffi::AnyBuffer logits, ffi::Buffer<ffi::DataType::U32> key,
+                                       ffi::Buffer<ffi::DataType::S32> dim0_offset, int64_t col_offset, int64_t k_cand,
+                                       int64_t vocab_total, int64_t rank, ffi::Span<const int64_t> exchange_of_rank,
+                                       ffi::Result<ffi::Buffer<ffi::DataType::S32>> order_token) {
+  const auto d = logits.dimensions();
+  if (d.size() != 2) return ffi::Error(ffi::ErrorCode::kInvalidArgument, "Only 2D inputs supported");
+  void* bufs[16];
+  const int world = (int)exchange_of_rank.size();
+  if (world < 1 || world > 16) return ffi::Error(ffi::ErrorCode::kInvalidArgument, "1 to 16 ranks");
+  for (int i = 0; i < world; ++i) bufs[i] = reinterpret_cast<void*>(exchange_of_rank[i]);
+  (void)order_token;
+  return as_error(tlx_exchange_shard_candidates(stream, logits.untyped_data(), dtype_of(logits.element_type()), d[0],
+                                                d[1], d[1], col_offset, (int)k_cand, /*noise=*/nullptr, 0,
+                                                key.typed_data(), 0u, 0u, vocab_total, 0, dim0_offset.typed_data(),
+                                                (int)rank, world, bufs));
+}
+
+ffi::Error ExchangeMergeAndSampleImpl(cudaStream_t stream, ffi::Buffer<ffi::DataType::S32> order_token,
+                                      ffi::Buffer<ffi::DataType::S32> top_k, ffi::Buffer<ffi::DataType::F32> top_p,
+                                      ffi::Buffer<ffi::DataType::F32> temperature, int64_t k_cand, int64_t world,
+                                      int64_t exchange, ffi::Result<ffi::Buffer<ffi::DataType::S32>> tokens,
+                                      ffi::Result<ffi::Buffer<ffi::DataType::S32>> status) {
+  (void)order_token;
+  const int64_t rows = (int64_t)top_k.element_count();
+  return as_error(tlx_exchange_merge_and_sample(stream, reinterpret_cast<void*>(exchange), rows, (int)k_cand, (int)world,
+                                                top_k.typed_data(), top_p.typed_data(), temperature.typed_data(),
+                                                tokens->typed_data(), status->typed_data()));
+}
+
 }  // namespace
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TlxExchangeShardCandidates, ExchangeShardCandidatesImpl,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .Arg<ffi::AnyBuffer>()
+                                  .Arg<ffi::Buffer<ffi::DataType::U32>>()
+                                  .Arg<ffi::Buffer<ffi::DataType::S32>>()
+                                  .Attr<int64_t>("col_offset")
+                                  .Attr<int64_t>("k_cand")
+                                  .Attr<int64_t>("vocab_total")
+                                  .Attr<int64_t>("rank")
+                                  .Attr<ffi::Span<const int64_t>>("exchange_of_rank")
+                                  .Ret<ffi::Buffer<ffi::DataType::S32>>());
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TlxExchangeMergeAndSample, ExchangeMergeAndSampleImpl,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .Arg<ffi::Buffer<ffi::DataType::S32>>()
+                                  .Arg<ffi::Buffer<ffi::DataType::S32>>()
+                                  .Arg<ffi::Buffer<ffi::DataType::F32>>()
+                                  .Arg<ffi::Buffer<ffi::DataType::F32>>()
+                                  .Attr<int64_t>("k_cand")
+                                  .Attr<int64_t>("world")
+                                  .Attr<int64_t>("exchange")
+                                  .Ret<ffi::Buffer<ffi::DataType::S32>>()
+                                  .Ret<ffi::Buffer<ffi::DataType::S32>>());
 
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TlxSample, SampleImpl,
                               ffi::Ffi::Bind()

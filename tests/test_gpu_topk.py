@@ -126,3 +126,47 @@ def test_topk_of_a_few_long_rows_split_over_ctas(cuda, rows, n, k, dtype):
                                  guarantee_convergence=True)
         ev, ei = o.top_dynamic_k(x, kk, k, replace_val=-1e12)
         assert exact_match(to_np(v), ev) and np.array_equal(to_np(i), ei)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("n,k", [(2048, 128), (18992, 50), (40001, 7), (70000, 128)])
+def test_topk_of_many_rows_two_pass_kernel(cuda, dtype, n, k):
+    # 256 rows and more with k <= 128 take the two-pass kernel (bound from group maxima); rows over 128 KB
+    # take the bound from a sample of the row.  One row each of the shapes that stress it: ascending and
+    # descending (the sampled bound is far too low or exact), one value only and two values (candidate
+    # overflow -> exact fallback), eighths (ties around the bound), NaNs, infinities, signed zeros, a row
+    # whose large values all sit in the part the sample skips.
+    rows = 260
+    rng = np.random.default_rng(n + k)
+    x = rng.standard_normal((rows, n)).astype(np.float32) * 2
+    x[0] = np.arange(n, dtype=np.float32) / 64
+    x[1] = np.arange(n, 0, -1).astype(np.float32) / 64
+    x[2] = 1.5
+    x[3] = rng.integers(0, 2, n).astype(np.float32)
+    x[4] = np.round(x[4] * 8) / 8
+    x[5, rng.random(n) < 0.01] = np.nan
+    x[6, rng.random(n) < 0.999] = -np.inf
+    x[7, ::5] = np.inf
+    x[8, ::7] = 0.0
+    x[8, 3::7] = -0.0
+    x[8] = np.minimum(x[8], 0.0)
+    x[9] = -np.abs(x[9])
+    x[9, 128:256] = 50.0 + np.arange(128, dtype=np.float32)      # only in the 2 KB pieces a sampled pass skips
+    x[10] = -np.inf
+    x[10, :k - 1] = 1.0                                            # fewer finite values than k
+    if dtype == "bf16":
+        x = x.astype(o.bfloat16)
+    elif dtype == "f16":
+        x = x.astype(np.float16)
+    _check_topk(cuda, x, k)
+
+
+def test_topk_two_pass_kernel_with_unaligned_rows(cuda):
+    # a row stride that is not a multiple of 16 bytes: the traversal's scalar head and tail
+    import torch
+    rng = np.random.default_rng(5)
+    base = rng.standard_normal((300, 5003)).astype(np.float32).astype(o.bfloat16)
+    xd = to_dev(base, cuda)[:, 1:5002]
+    v, i = tax.top_k(xd, 33, block_token=1)
+    ev, ei = o.top_k(np.ascontiguousarray(base[:, 1:5002]), 33)
+    assert np.array_equal(to_np(i), ei) and exact_match(to_np(v), ev)
