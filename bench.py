@@ -476,6 +476,29 @@ def run_op_workload(args):
         ind = torch.randint(0, n, (rows, 4096), generator=g, device=dev, dtype=torch.int32)
         fn = lambda i: tumpy.take_along_axis(x, ind, axis=1)
         algo, note = 3 * rows * 4096 * 4, "indices + gathered elements + output (32-byte sectors: 134 217 728 B)"
+    elif w in ("c5-shard-of-8", "c5-merge-of-8"):
+        # what ONE rank of an 8-way vocabulary split does per step, on one GPU: the candidate stage on its
+        # bf16 [rows, 18992] shard, or the merge of 8 ranks' candidate blocks (k' = 50 each) and the tail.
+        # rows = 1024 is configuration 5; --rows scales it (4096 rows make the shard larger than L2).
+        from tallax_b200._src import ops
+        rows, n, k = (args.rows or 1024), 151936 // 8, 50
+        g.manual_seed(4)
+        nz = torch.rand((rows, n), generator=g, device=dev)
+        shards = [(torch.randn((rows, n), generator=g, device=dev) * 2).to(torch.bfloat16) for _ in range(8)]
+        gathered = torch.empty((8, 3, rows, k), dtype=torch.float32, device=dev)
+        for r in range(8):
+            ops.shard_candidates(shards[r], r * n, k, noise_shard=nz, out=gathered[r])
+        blk = torch.empty((3, rows, k), dtype=torch.float32, device=dev)
+        tok = torch.empty(rows, dtype=torch.int32, device=dev)
+        tk = torch.full((rows,), k, dtype=torch.int32, device=dev)
+        tp = torch.full((rows,), 0.95, device=dev)
+        T = torch.full((rows,), 0.8, device=dev)
+        if w == "c5-shard-of-8":
+            fn = lambda i: ops.shard_candidates(shards[i % 8], 0, k, noise_shard=nz, out=blk)
+            algo, note = rows * n * 2 + rows * k * 12, "the shard once + its candidates out"
+        else:
+            fn = lambda i: ops.merge_and_sample(gathered, tk, tp, T, out=tok)
+            algo, note = 8 * rows * k * 12 + rows * 4, "8 candidate blocks once + the tokens (latency-bound: 0.6 KB per row and rank)"
     else:
         raise SystemExit(f"unknown workload {w}")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
@@ -498,7 +521,7 @@ def run_op_workload(args):
     print(json.dumps({
         "metric": "rows_per_s", "value": rows / (ms / 1e3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "vs_baseline": None, "dtype": "bf16" if w.startswith("c5") else "f32", "data": "synthetic",
         "config": {"workload": w, "rows": rows, "row_length": n, "l2": "256 MB flush buffer written between steps"},
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -656,9 +679,11 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time plain library calls instead of CUDA graph launches")
     ap.add_argument("--rows-per-call", type=int, default=0, choices=[0, 32, 64, 128],
                     help="time calls of this many rows instead of 256 (the small-batch paths)")
+    ap.add_argument("--rows", type=int, default=0, help="row count of the c5-shard-of-8 / c5-merge-of-8 workloads")
     ap.add_argument("--workload", default="c3", help="c3 (default, the fused sampler) | c1 | c2 | c4a | "
                     "c4a-single-pass | c4b: the other operators at their benchmark sizes, one GPU, rows/s | c5: the "
-                    "vocab-sharded sampler over the ranks of torchrun")
+                    "vocab-sharded sampler over the ranks of torchrun | c5-shard-of-8, c5-merge-of-8: one rank's "
+                    "two stages of an 8-way vocabulary split, on one GPU")
     args = ap.parse_args()
     if args.workload == "c5" and args.impl == "ours":
         run_vocab_sharded(args)

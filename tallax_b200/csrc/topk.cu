@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
   const int sub = n * (int64_t)sizeof(T) > (128 << 10) ? 4 : 1;
   GroupMax<DT> gm;
   gm.init();
-  for_each_vec<DT, 8>(row, n, sub, [&](const uint4& v, int64_t) { gm.add(v); }, [&](T x, int64_t) { gm.add_one(x); });
+  for_each_vec<DT, 10>(row, n, sub, [&](const uint4& v, int64_t) { gm.add(v); }, [&](T x, int64_t) { gm.add_one(x); });
 #pragma unroll
   for (int j = 0; j < kSlots; ++j) gkeys[threadIdx.x * kSlots + j] = (uint16_t)(f32_key(gm.slot(j)) >> 16);
   if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
   if constexpr (DT == TLX_BF16) {
     const __nv_bfloat16 tb = __ushort_as_bfloat16((unsigned short)(__float_as_uint(thr) >> 16));
     const __nv_bfloat162 t2 = __halves2bfloat162(tb, tb);
-    for_each_vec<DT, 8>(row, n, 1,
+    for_each_vec<DT, 10>(row, n, 1,
       [&](const uint4& v, int64_t cb) {
         const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
         // __hblt2: both halves less than the bound (false when either is a NaN)
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
       },
       push_one);
   } else if constexpr (DT == TLX_F16) {
-    for_each_vec<DT, 8>(row, n, 1,
+    for_each_vec<DT, 10>(row, n, 1,
       [&](const uint4& v, int64_t cb) {
         const __half2* e = reinterpret_cast<const __half2*>(&v);
         bool any = false;
@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
       },
       push_one);
   } else {
-    for_each_vec<DT, 8>(row, n, 1,
+    for_each_vec<DT, 10>(row, n, 1,
       [&](const uint4& v, int64_t cb) {
         const float* e = reinterpret_cast<const float*>(&v);
         if (!(e[0] < thr) || !(e[1] < thr) || !(e[2] < thr) || !(e[3] < thr)) note(cb);
