@@ -211,6 +211,20 @@ def run_ours(args):
 
     rows_call = args.rows_per_call or B   # 32 / 64 / 128: the same rows in smaller calls (a smaller decode batch)
     sets = [make_inputs(torch, device, seed=1000 * rank + s, rows=rows_call) for s in range(N_SETS)]
+    if args.mix != "c3":
+        # the same logits and noise with another mix of sampling parameters (kernel time only, one GPU)
+        def remix(s):
+            x, tk, tp, T, u = s
+            if args.mix == "greedy":
+                T = torch.zeros_like(T)
+            elif args.mix in ("k1", "k50", "k1024"):
+                tk = torch.full_like(tk, int(args.mix[1:]))
+            elif args.mix == "no-wide":
+                tk = torch.where(tk == 0, torch.full_like(tk, 500), tk)
+            elif args.mix == "all-wide":
+                tk = torch.zeros_like(tk)
+            return (x, tk, tp, T, u)
+        sets = [remix(s) for s in sets]
     ws = ops.SampleWorkspace(rows_call, V, device)
     meta = [sampling.SamplingMetadata(top_k=s[1], top_p=s[2], temperature=s[3]) for s in sets]
 
@@ -273,6 +287,24 @@ def run_ours(args):
         r1.record()
         barrier()
         replay_ms = r0.elapsed_time(r1) / 200
+
+    if args.mix != "c3":
+        if rank == 0:
+            per_step = ms / args.steps
+            peak, peak_src = peaks()
+            algo = rows_call * V * 2 + rows_call * 16
+            print(json.dumps({
+                "metric": METRIC, "value": rows_call / (per_step / 1e3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": dict(bench_config(rows_call, 1), mix=args.mix),
+                "clocks": clocks.summary(), "gpu_launches": int(launches),
+                "replay_200": {"ms_per_step": replay_ms},
+                "roofline": {"bound": "hbm", "achieved": algo / (per_step / 1e3) / 1e9, "peak": peak, "unit": "GB/s",
+                             "frac": algo / (per_step / 1e3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                             "note": "logits once + parameters + tokens; kernel time only, no end-to-end or CPU leg"}}),
+                  flush=True)
+        return
 
     # ---- end to end through the public API from pinned host buffers --------------------------
     h_logits = torch.empty((rows_call, V), dtype=torch.bfloat16).pin_memory()
@@ -679,6 +711,10 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time plain library calls instead of CUDA graph launches")
     ap.add_argument("--rows-per-call", type=int, default=0, choices=[0, 32, 64, 128],
                     help="time calls of this many rows instead of 256 (the small-batch paths)")
+    ap.add_argument("--mix", default="c3", choices=["c3", "greedy", "k1", "k50", "k1024", "no-wide", "all-wide"],
+                    help="c3 (default): the benchmark's parameter mix; the others keep its logits and noise and set "
+                         "temperature 0 / top_k 1, 50, 1024 for every row / top_k 500 for the rows without top-k / "
+                         "no top-k for any row (one GPU, kernel time only)")
     ap.add_argument("--rows", type=int, default=0, help="row count of the c5-shard-of-8 / c5-merge-of-8 workloads")
     ap.add_argument("--workload", default="c3", help="c3 (default, the fused sampler) | c1 | c2 | c4a | "
                     "c4a-single-pass | c4b: the other operators at their benchmark sizes, one GPU, rows/s | c5: the "
