@@ -95,3 +95,26 @@ def test_device_operand_entry_points_reject_missing_key_without_gpu():
     assert rc == _lib.TLX_ERR_INVALID and b"key" in lib.tlx_last_error()
     rc = lib.tlx_gumbel_argmax_dev(None, None, None, None, 4, 4, None, 16, 1, None)
     assert rc == _lib.TLX_ERR_INVALID
+
+
+def test_exchange_layout_and_argument_errors_need_no_gpu():
+    import ctypes
+    lib = _lib.load()
+    # header (256 B) + two sets of (arrival words, world * 3 * rows * k floats), each padded to 256 B
+    rows, k, world = 1024, 50, 8
+    flags = (rows * 4 + 255) // 256 * 256
+    cand = (world * 3 * rows * k * 4 + 255) // 256 * 256
+    assert lib.tlx_exchange_bytes(rows, k, world) == 256 + 2 * (flags + cand)
+    assert lib.tlx_exchange_bytes(rows, k, 17) == 0 and lib.tlx_exchange_bytes(0, k, 2) == 0
+    bufs = (ctypes.c_void_p * 2)(None, None)
+    # rank outside the world, and a missing buffer: rejected before any CUDA call
+    rc = lib.tlx_exchange_shard_candidates(None, None, _lib.TLX_BF16, 4, 64, 64, 0, 8, None, 0, None, 0, 0, 128, 0, None,
+                                           2, 2, bufs)
+    assert rc == _lib.TLX_ERR_INVALID and b"rank" in lib.tlx_last_error()
+    rc = lib.tlx_exchange_shard_candidates(None, None, _lib.TLX_BF16, 4, 64, 64, 0, 8, None, 0, None, 0, 0, 128, 0, None,
+                                           0, 2, bufs)
+    assert rc == _lib.TLX_ERR_INVALID and b"buffer of rank 0" in lib.tlx_last_error()
+    rc = lib.tlx_exchange_merge_and_sample(None, None, 4, 8, 2, None, None, None, None, None)
+    assert rc == _lib.TLX_ERR_INVALID
+    rc = lib.tlx_exchange_merge_and_sample(None, None, 4, 1024, 16, None, None, None, None, None)
+    assert rc == _lib.TLX_ERR_UNSUPPORTED

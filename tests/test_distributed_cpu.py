@@ -52,6 +52,37 @@ def _install_cpu_kernels():
     ops.shard_candidates = shard_candidates
     ops.merge_and_sample = merge_and_sample
 
+    # The peer-memory exchange: the buffers become host objects and a rank's stores into its peers' buffers an
+    # all-gather at merge time; what stays under test is make_vocab_exchange (handles gathered in rank order,
+    # own entry not opened) and the routing of sample_vocab_sharded(..., exchange=).
+    class Exchange:
+        def __init__(self, rows, k_cand, world):
+            self.rows, self.k_cand, self.world, self.rank, self.block, self.seen = rows, k_cand, world, None, None, None
+
+        @classmethod
+        def create(cls, rows, k_cand, world, device=None):
+            self = cls(rows, k_cand, world)
+            self.handle = b"buffer of rank %d" % dist.get_rank()
+            return self
+
+        def attach(self, rank, handles):
+            self.rank, self.seen = rank, list(handles)
+            return self
+
+    def exchange_shard_candidates(logits_shard, col_offset, exchange, *, noise_shard=None, rng_key=None,
+                                  vocab_total=None, dim0_offset=0):
+        exchange.block = shard_candidates(logits_shard, col_offset, exchange.k_cand, noise_shard=noise_shard)
+        exchange.args = (col_offset, vocab_total)
+
+    def exchange_merge_and_sample(exchange, top_k_, top_p, temperature, out=None):
+        gathered = torch.empty((exchange.world,) + tuple(exchange.block.shape), dtype=torch.float32)
+        dist.all_gather_into_tensor(gathered.view((exchange.world * 3,) + tuple(exchange.block.shape[1:])), exchange.block)
+        return merge_and_sample(gathered, top_k_, top_p, temperature, out=out)
+
+    ops.Exchange = Exchange
+    ops.exchange_shard_candidates = exchange_shard_candidates
+    ops.exchange_merge_and_sample = exchange_merge_and_sample
+
 
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -69,6 +100,14 @@ def _worker(rank, world, port, q):
         tok = sampling.sample_vocab_sharded(None, torch.from_numpy(x[:, rank * vl:(rank + 1) * vl].copy()), md,
                                             noise_shard=torch.from_numpy(noise[:, rank * vl:(rank + 1) * vl].copy()),
                                             k_cand=32)
+        # the same step through the exchange form
+        ex = sampling.make_vocab_exchange(B, 32)
+        assert ex.rank == rank and ex.seen == [b"buffer of rank 0", b"buffer of rank 1"]
+        tok2 = sampling.sample_vocab_sharded(None, torch.from_numpy(x[:, rank * vl:(rank + 1) * vl].copy()), md,
+                                             noise_shard=torch.from_numpy(noise[:, rank * vl:(rank + 1) * vl].copy()),
+                                             k_cand=32, exchange=ex)
+        assert ex.args == (rank * vl, V)
+        assert tok2.tolist() == tok.tolist()
         q.put((rank, tok.numpy().tolist()))
     finally:
         dist.destroy_process_group()
