@@ -649,9 +649,43 @@ def vocab_sharded_record(args, torch, dist, device, rank, world, steps=30):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) / steps
 
+    # Steps queued back to back, as a decode loop issues them: no barrier and no host synchronisation between
+    # steps, four rotating copies of the shard (rows rolled) so that every step reads from HBM once the four
+    # shards exceed L2 (8 ranks: 4 x 39 MB of logits; the step's other reads are gathers).  One CUDA graph per
+    # copy; the time per step is (last step's end - first step's start) / steps, max over ranks.
+    def timed_back_to_back(n_steps=200):
+        shards4 = [shard] + [torch.roll(shard, j, dims=0) for j in (1, 2, 3)]
+        noise4 = [nshard] + [torch.roll(nshard, j, dims=0) for j in (1, 2, 3)]
+        graphs = []
+        for j in range(4):
+            sampling.sample_vocab_sharded(None, shards4[j], md, noise_shard=noise4[j], k_cand=k, workspace=vws,
+                                          exchange=exchange)
+        barrier()
+        for j in range(4):
+            gj = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gj):
+                sampling.sample_vocab_sharded(None, shards4[j], md, noise_shard=noise4[j], k_cand=k, workspace=vws,
+                                              exchange=exchange)
+            graphs.append(gj)
+        for j in range(4):          # every rank replays the same sequence: the exchange stays in step
+            graphs[j].replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n_steps):
+            graphs[i % 4].replay()
+        e1.record()
+        e1.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        barrier()
+        return float(t.item()) / n_steps
+
     ms_g, _, launches_g, tok_g = timed(step_gathered)
     ms, clocks, launches, tok = timed(step_exchange)
     ms_graph = timed_graph()
+    ms_b2b = timed_back_to_back()
     ex_steps, ex_error = exchange.state()
     barrier()
     if rank == 0:
@@ -676,6 +710,10 @@ def vocab_sharded_record(args, torch, dist, device, rank, world, steps=30):
         "parity": f"{mismatches} of {rows} tokens differ from the unsharded fused sampler on rank 0",
         "exchange_state": {"steps": ex_steps, "error": ex_error},
         "graph_replay_ms_per_step": ms_graph,
+        "back_to_back": {"ms_per_step": ms_b2b, "value": rows / (ms_b2b / 1e3), "unit": UNIT, "steps": 200,
+                         "note": "200 steps queued back to back as CUDA-graph replays (no barrier or host "
+                                 "synchronisation between steps; four rotating copies of the shard); the figures "
+                                 "above it are per-step latencies, each step started from idle after a barrier"},
         "nccl_all_gather": {"ms_per_step": ms_g, "gpu_launches": launches_g, "mismatches": mismatches_g,
                             "note": "the same step with torch.distributed all_gather_into_tensor between the two "
                                     "kernels"},
