@@ -1791,12 +1791,14 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
-// Number of entries of the ascending list blk[0..len) that are smaller than c.
-__device__ __forceinline__ int count_below(const uint64_t* blk, int len, uint64_t c) {
+// Number of entries of the ascending list blk[0..len) whose high word is smaller than `target`.  The high
+// word is the inverted key; it never reaches 0xFFFFFFFF (no key is 0), so target may be a high word plus one.
+__device__ __forceinline__ int count_high_below(const uint64_t* blk, int len, uint32_t target) {
+  const uint32_t* hi = reinterpret_cast<const uint32_t*>(blk) + 1;
   int lo = 0;
   while (len > 0) {
     const int half = len >> 1;
-    if (blk[lo + half] < c) { lo += half + 1; len -= half + 1; }
+    if (hi[2 * (lo + half)] < target) { lo += half + 1; len -= half + 1; }
     else len = half;
   }
   return lo;
@@ -1848,7 +1850,14 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
   v += r * p.row_stride;
   id += r * p.row_stride;
   un += r * p.row_stride;
-  auto at = [&](uint32_t i) { return (int64_t)(i / kpb) * p.block_stride + (int64_t)(i % kpb); };
+  // block of candidate i without an integer division: (i + 0.5) / kpb is at least 0.5 / kpb away from an
+  // integer and i < 8192, far more than the product's rounding error
+  const float inv_kpb = 1.0f / (float)kpb;
+  auto block_of = [&](uint32_t i) { return (int)(((float)i + 0.5f) * inv_kpb); };
+  auto at = [&](uint32_t i) {
+    const int b = block_of(i);
+    return (int64_t)b * p.block_stride + (int64_t)((int)i - b * kpb);
+  };
   // low word = position in the gathered list: shards are laid side by side in ascending
   // token order, so position order equals token order among equal values
   int unsorted = 0;
@@ -1858,7 +1867,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n_cand; i += blockDim.x)
-    if (i % kpb && cand[i - 1] > cand[i]) unsorted = 1;
+    if (i != block_of(i) * kpb && cand[i - 1] > cand[i]) unsorted = 1;
   unsorted = __syncthreads_or(unsorted);
   int K = p.top_k[r];
   if (K <= 0 || K > n_cand) K = n_cand;
@@ -1874,7 +1883,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
     if (threadIdx.x == 0) s.fill = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
-      const int b = i / kpb;
+      const int b = block_of(i);
       const int q = i - b * kpb;
       if (q >= K) continue;
       const uint64_t c = cand[i];
@@ -1888,13 +1897,16 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
     const int nlisted = s.fill;
     for (int l = threadIdx.x; l < nlisted; l += blockDim.x) {
       const int i = (int)listed[l];
-      const int b = i / kpb;
+      const int b = block_of(i);
       const int q = i - b * kpb;
       const uint64_t c = cand[i];
       int place = q;
       const int span = min(kpb, K - q);   // a block's entries from `span` on cannot change the verdict
+      // entries of another block that precede c: a smaller high word (the inverted key), or an equal one in a
+      // block before c's own (positions, the low words, grow with the block) -- a search on the high words
+      const uint32_t chi = (uint32_t)(c >> 32);
       for (int o = 0; o < blocks && place < K; ++o)
-        if (o != b) place += count_below(cand + o * kpb, span, c);
+        if (o != b) place += count_high_below(cand + o * kpb, span, chi + (o < b ? 1u : 0u));
       if (place < K) merged[place] = c;
     }
     __syncthreads();
