@@ -304,9 +304,34 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
 
   // rows that L2 would not keep between the passes give their bound from a quarter of the row
   const int sub = n * (int64_t)sizeof(T) > (128 << 10) ? 4 : 1;
+  // bf16 rows of up to 4096 vectors (64 KB) read in full by pass 1: pass 1 also leaves every vector's greatest
+  // element (NaN if it holds one) in shared memory, in the candidate list's space, and pass 2 reads those
+  // 2 bytes per vector instead of the row
+  constexpr int VEC = 16 / (int)sizeof(T);
+  int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(row) & 15)) & 15) / sizeof(T));
+  if (head > n) head = n;
+  const int64_t nvec = (n - head) / VEC;
+  bool vec_maxima = false;
+  if constexpr (DT == TLX_BF16) vec_maxima = sub == 1 && nvec <= kShortCap * 4;
+  __nv_bfloat16* vmax = reinterpret_cast<__nv_bfloat16*>(cand);
   GroupMax<DT> gm;
   gm.init();
-  for_each_vec<DT, 10>(row, n, sub, [&](const uint4& v, int64_t) { gm.add(v); }, [&](T x, int64_t) { gm.add_one(x); });
+  if constexpr (DT == TLX_BF16) {
+    if (vec_maxima) {
+      const __nv_bfloat16 ninf = __float2bfloat16_rn(-INFINITY);
+      for (int64_t i = nvec + threadIdx.x; i < ((nvec + 7) & ~(int64_t)7); i += blockDim.x) vmax[i] = ninf;
+      for_each_vec<DT, 10>(row, n, 1,
+        [&](const uint4& v, int64_t cb) {
+          gm.add(v);
+          const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
+          const __nv_bfloat162 a = __hmax2_nan(__hmax2_nan(e[0], e[1]), __hmax2_nan(e[2], e[3]));
+          vmax[(cb - head) >> 3] = __hmax_nan(__low2bfloat16(a), __high2bfloat16(a));
+        },
+        [&](T x, int64_t) { gm.add_one(x); });
+    }
+  }
+  if (!vec_maxima)
+    for_each_vec<DT, 10>(row, n, sub, [&](const uint4& v, int64_t) { gm.add(v); }, [&](T x, int64_t) { gm.add_one(x); });
 #pragma unroll
   for (int j = 0; j < kSlots; ++j) gkeys[threadIdx.x * kSlots + j] = (uint16_t)(f32_key(gm.slot(j)) >> 16);
   if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
@@ -337,13 +362,30 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
   if constexpr (DT == TLX_BF16) {
     const __nv_bfloat16 tb = __ushort_as_bfloat16((unsigned short)(__float_as_uint(thr) >> 16));
     const __nv_bfloat162 t2 = __halves2bfloat162(tb, tb);
-    for_each_vec<DT, 10>(row, n, 1,
-      [&](const uint4& v, int64_t cb) {
-        const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
-        // __hblt2: both halves less than the bound (false when either is a NaN)
-        if (!(__hblt2(e[0], t2) && __hblt2(e[1], t2) && __hblt2(e[2], t2) && __hblt2(e[3], t2))) note(cb);
-      },
-      push_one);
+    if (vec_maxima) {
+      // eight vectors' maxima per 16-byte load; the few elements before and after the aligned body are
+      // pushed after the barrier below (the candidate list shares its space with the maxima)
+      const uint4* vm4 = reinterpret_cast<const uint4*>(vmax);
+      const int groups = (int)((nvec + 7) >> 3);
+      for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        const uint4 w = vm4[g];
+        const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&w);
+        if (!(__hblt2(e[0], t2) && __hblt2(e[1], t2) && __hblt2(e[2], t2) && __hblt2(e[3], t2))) {
+          const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(&w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (g * 8 + j < nvec && !__hlt(x[j], tb)) note(head + ((int64_t)g * 8 + j) * VEC);   // not the padding
+        }
+      }
+    } else {
+      for_each_vec<DT, 10>(row, n, 1,
+        [&](const uint4& v, int64_t cb) {
+          const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
+          // __hblt2: both halves less than the bound (false when either is a NaN)
+          if (!(__hblt2(e[0], t2) && __hblt2(e[1], t2) && __hblt2(e[2], t2) && __hblt2(e[3], t2))) note(cb);
+        },
+        push_one);
+    }
   } else if constexpr (DT == TLX_F16) {
     for_each_vec<DT, 10>(row, n, 1,
       [&](const uint4& v, int64_t cb) {
@@ -366,6 +408,10 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
       push_one);
   }
   __syncthreads();
+  if (vec_maxima) {
+    for (int64_t c = threadIdx.x; c < head; c += blockDim.x) push_one(row[c], c);
+    for (int64_t c = head + nvec * VEC + threadIdx.x; c < n; c += blockDim.x) push_one(row[c], c);
+  }
   if (*nnoted > kShortCap) {
     if (threadIdx.x == 0) s.fill = kShortCap + 1;   // more vectors than the list holds: the exact fallback
   } else {

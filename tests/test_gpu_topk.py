@@ -170,3 +170,43 @@ def test_topk_two_pass_kernel_with_unaligned_rows(cuda):
     v, i = tax.top_k(xd, 33, block_token=1)
     ev, ei = o.top_k(np.ascontiguousarray(base[:, 1:5002]), 33)
     assert np.array_equal(to_np(i), ei) and exact_match(to_np(v), ev)
+
+
+_FORCED_CHILD = r"""
+import sys
+sys.path.insert(0, %r)
+import numpy as np, torch
+from oracle import tallax_oracle as o
+from tallax_b200 import tax
+from tests.conftest import exact_match, to_dev, to_np
+dev = torch.device("cuda", 0)
+rng = np.random.default_rng(11)
+for dtype in ("bf16", "f16", "f32"):
+    for rows, n, k in [(5, 520, 50), (7, 100, 100), (3, 8, 8), (9, 2060, 128), (4, 1031, 17), (2, 33000, 64)]:
+        x = rng.standard_normal((rows, n)).astype(np.float32)
+        x[0, k - 1:] = -np.inf                 # fewer finite values than k: the bound is the bin of -inf
+        if rows > 1:
+            x[1] = np.round(x[1] * 4) / 4      # ties
+        if rows > 2:
+            x[2, ::3] = np.nan
+        x = x.astype(o.bfloat16) if dtype == "bf16" else x.astype(np.float16) if dtype == "f16" else x
+        v, i = tax.top_k(to_dev(x, dev), k, block_token=1)
+        ev, ei = o.top_k(x, k)
+        assert np.array_equal(to_np(i), ei), (dtype, rows, n, k)
+        assert exact_match(to_np(v), ev), (dtype, rows, n, k)
+print("ok")
+"""
+
+
+def test_two_pass_kernel_forced_on_small_and_odd_shapes(cuda):
+    # TLX_TOPK_PATH=short (read once per process, hence the child) sends every eligible call through the
+    # two-pass kernel, also shapes the heuristic would keep away from it: rows shorter than a vector, vector
+    # counts that are no multiple of eight (padding of the per-vector maxima), a bound in the bin of -inf
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TLX_TOPK_PATH="short")
+    res = subprocess.run([sys.executable, "-c", _FORCED_CHILD % root], capture_output=True, text=True, env=env,
+                         timeout=600)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]
