@@ -245,43 +245,49 @@ static __device__ __noinline__ void push_vector(uint4 v, int64_t cb, uint32_t t1
 }
 
 // The K-th largest of the G 16-bit keys in shared memory (1 <= K <= G): two counting passes of 8 bits.
-// hist: 256 words, scan: 40 words, pick: 2 words, all in shared memory.  All threads call; blockDim
-// divides 256.
-static __device__ __noinline__ uint32_t kth_largest_u16(const uint16_t* keys, int G, int K, uint32_t* hist,
-                                                    uint32_t* scan, int* pick) {
-  const int per = 256 / blockDim.x;
-  uint32_t prefix = 0;
-  int need = K;
-  for (int pass = 0; pass < 2; ++pass) {
-    const int sh = pass ? 0 : 8;
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < G; i += blockDim.x) {
-      const uint32_t k = keys[i];
-      if (pass == 0 || (k >> 8) == prefix) atomicAdd(&hist[(k >> sh) & 255u], 1u);
-    }
-    __syncthreads();
-    const int hi = 255 - threadIdx.x * per;   // thread t owns bins hi, hi-1, ... (descending)
-    uint32_t local = 0;
-    for (int j = 0; j < per; ++j) local += hist[hi - j];
-    uint32_t total;
-    const uint32_t incl = block_scan_incl<uint32_t>(local, scan, &total, ShflUpU32());
-    const uint32_t excl = incl - local;
-    if (excl < (uint32_t)need && incl >= (uint32_t)need) {
-      uint32_t run = excl;
-      for (int j = 0; j < per; ++j) {
-        const uint32_t c = hist[hi - j];
-        if (run + c >= (uint32_t)need) { pick[0] = hi - j; pick[1] = (int)run; break; }
-        run += c;
-      }
-    }
-    __syncthreads();
-    const int b = pick[0], above = pick[1];
-    __syncthreads();
-    prefix = pass ? ((prefix << 8) | (uint32_t)b) : (uint32_t)b;
-    need -= above;
+// hist: 512 words (one histogram per pass), pick: 4 words, both in shared memory.  All threads call.  The
+// bin that holds the `need`-th largest is found by warp 0 alone (eight bins per lane, one shuffle scan):
+// five CTA barriers in all.
+__device__ __forceinline__ void warp_pick_bin(const uint32_t* h, int need, int* out) {
+  const int lane = lane_id();
+  const int hi = 255 - 8 * lane;   // lane l owns bins hi, hi-1, ..., hi-7 (descending)
+  uint32_t local = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) local += h[hi - j];
+  uint32_t incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += up;
   }
-  return prefix;
+  const uint32_t excl = incl - local;
+  if (excl < (uint32_t)need && incl >= (uint32_t)need) {
+    uint32_t run = excl;
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t c = h[hi - j];
+      if (run + c >= (uint32_t)need) { out[0] = hi - j; out[1] = (int)run; break; }
+      run += c;
+    }
+  }
+}
+
+static __device__ __noinline__ uint32_t kth_largest_u16(const uint16_t* keys, int G, int K, uint32_t* hist, int* pick) {
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < G; i += blockDim.x) atomicAdd(&hist[keys[i] >> 8], 1u);
+  __syncthreads();
+  if (warp_id() == 0) warp_pick_bin(hist, K, pick);
+  __syncthreads();
+  const uint32_t top = (uint32_t)pick[0];
+  const int need = K - pick[1];
+  for (int i = threadIdx.x; i < G; i += blockDim.x) {
+    const uint32_t k = keys[i];
+    if ((k >> 8) == top) atomicAdd(&hist[256 + (k & 255u)], 1u);
+  }
+  __syncthreads();
+  if (warp_id() == 0) warp_pick_bin(hist + 256, need, pick + 2);
+  __syncthreads();
+  return (top << 8) | (uint32_t)pick[2];
 }
 
 template <int DT>
@@ -294,7 +300,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
   uint64_t* cand = reinterpret_cast<uint64_t*>(smem_raw + ((sizeof(SelectShared) + 15) & ~size_t(15)));
   // the group keys and the small histogram live in the big histogram's space, which only the fallback uses
   uint16_t* gkeys = reinterpret_cast<uint16_t*>(s.hist);            // G * 2 bytes <= 2 KB
-  uint32_t* hist8 = s.hist + 1024;                                    // 256 words
+  uint32_t* hist8 = s.hist + 1024;                                    // 512 words
   const int64_t r = blockIdx.x;
   const T* row = reinterpret_cast<const T*>(p.x) + r * p.row_stride;
   const int K = p.k_max;
@@ -336,7 +342,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
   for (int j = 0; j < kSlots; ++j) gkeys[threadIdx.x * kSlots + j] = (uint16_t)(f32_key(gm.slot(j)) >> 16);
   if (threadIdx.x == 0) { s.fill = 0; s.bin = 0; s.above = 0; s.refinements = 0; }
   __syncthreads();
-  const uint32_t t16 = kth_largest_u16(gkeys, G, K, hist8, s.scan_u32, s.tmp_i);
+  const uint32_t t16 = kth_largest_u16(gkeys, G, K, hist8, s.tmp_i);
   // lower edge of the bound's 16-bit bin as a value; a NaN pattern (the bin of -inf) admits everything
   const float thr = key_f32(t16 << 16);
 
@@ -352,7 +358,7 @@ __global__ void __launch_bounds__(kShortThreads, 8) topk_short_kernel(TopkParams
   // The streaming loop only notes which vectors hold an element at or above the bound (about one per
   // candidate); the noted vectors are then read again, one per thread, and their elements pushed.
   uint32_t* noted = s.hist + 2048;          // up to kShortCap first columns, in the fallback's histogram space
-  int* nnoted = &s.tmp_i[2];
+  int* nnoted = &s.above;                   // (tmp_i holds the bound's picks, which threads may still be reading)
   if (threadIdx.x == 0) *nnoted = 0;
   __syncthreads();
   auto note = [&](int64_t cb) {
