@@ -1891,6 +1891,16 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
       bool out = false;
       if (probe < kpb)
         for (int o = 0; o < blocks && !out; ++o) out = o != b && cand[o * kpb + probe] < c;
+      if (!out) {
+        // the same with the places shared out evenly: if entry d-1 of EVERY other block precedes it, with
+        // d * (blocks - 1) >= K - q, its place is K or more as well
+        const int d = (K - q + blocks - 2) / (blocks - 1);
+        if (d - 1 < kpb) {
+          bool all = true;
+          for (int o = 0; o < blocks && all; ++o) all = o == b || cand[o * kpb + d - 1] < c;
+          out = all;
+        }
+      }
       if (!out) listed[atomicAdd(&s.fill, 1)] = (uint32_t)i;
     }
     __syncthreads();
