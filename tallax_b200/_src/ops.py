@@ -428,6 +428,7 @@ class Exchange:
         return steps.value, err.value
 
     def close(self):
+        """Unmaps the other ranks' buffers and frees this rank's own (no rank may still write to it)."""
         lib = _lib.load()
         for p in self._opened:
             lib.tlx_exchange_close(p)
@@ -435,6 +436,12 @@ class Exchange:
         if self.own:
             lib.tlx_exchange_destroy(self.own)
             self.own = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:      # interpreter shutdown: the library or the CUDA context may be gone already
+            pass
 
 
 def exchange_shard_candidates(logits_shard, col_offset: int, exchange: Exchange, *, noise_shard=None, rng_key=None,

@@ -96,3 +96,49 @@ def test_a_missing_rank_is_reported_not_waited_for_forever(cuda):
     finally:
         for e in group:
             e.close()
+
+
+def test_exchange_steps_replayed_from_a_cuda_graph(cuda):
+    """The set a step uses is the low bit of a counter in the buffer that the merge kernel advances: a captured
+    step can be replayed any number of times, interleaved with eager steps, without host bookkeeping."""
+    import torch
+    from tallax_b200._src import ops
+    from tests.conftest import to_dev
+
+    dev = torch.device("cuda", 0)
+    B, V, k = 40, 8192, 32
+    (ex,) = ops.Exchange.local_group(B, k, 1, dev)
+    try:
+        inputs = []
+        for seed in (21, 22, 23, 24):
+            x, tk, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=seed, dtype="bf16")
+            tk = np.minimum(tk, k).astype(np.int32)
+            exp, flags = o.sample(x, tk, tp, T, noise=noise, return_flags=True)
+            inputs.append((to_dev(x, dev), to_dev(noise, dev), exp, flags))
+        dtk, dtp, dT = to_dev(tk, dev), to_dev(tp, dev), to_dev(T, dev)
+        sx, sn = torch.empty_like(inputs[0][0]), torch.empty_like(inputs[0][1])
+        out = torch.empty(B, dtype=torch.int32, device=dev)
+
+        def step():
+            ops.exchange_shard_candidates(sx, 0, ex, noise_shard=sn, vocab_total=V)
+            ops.exchange_merge_and_sample(ex, dtk, dtp, dT, out=out)
+
+        sx.copy_(inputs[0][0]); sn.copy_(inputs[0][1])
+        step()                                   # eager: step 1 (also loads the kernels before the capture)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()                               # captured, not run
+        done = 1
+        for j, (x, noise, exp, flags) in enumerate(inputs):
+            sx.copy_(x); sn.copy_(noise)
+            if j == 2:
+                step()                           # an eager step between replays
+            else:
+                graph.replay()
+            done += 1
+            got = out.cpu().numpy()
+            assert not ((got != exp) & ~flags).any(), j
+            assert ex.state() == (done, 0)
+    finally:
+        ex.close()
