@@ -274,7 +274,9 @@ int tlx_merge_and_sample(void* stream, const float* cand_vals, const int32_t* ca
  * same sequence of calls (one tlx_exchange_shard_candidates, then one
  * tlx_exchange_merge_and_sample, per step); the ranks must have finished creating and mapping
  * the buffers (a host barrier) before the first step.  After a wait gave up the buffers are out
- * of step: destroy and recreate them.
+ * of step: destroy and recreate them.  A call whose rows, k_cand or world are not those the buffer
+ * was created with touches no buffer: the error word becomes 2, stage 2 sets *out_status = 2 and
+ * writes token -1.
  *
  * tlx_exchange_create allocates and clears this rank's buffer (the one allocation the library makes:
  * an inter-process handle covers a whole device allocation) and writes its handle, which the other

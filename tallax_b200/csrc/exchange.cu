@@ -22,6 +22,13 @@ int tlx_exchange_create(int64_t rows, int k_cand, int world, void** exchange, un
   cudaError_t e = cudaMalloc(&buf, bytes);
   if (e != cudaSuccess) return set_error(TLX_ERR_CUDA, "exchange_create: cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
   e = cudaMemset(buf, 0, bytes);
+  if (e == cudaSuccess) {
+    ExchangeHeader h{};
+    h.rows = (uint32_t)rows;
+    h.k_cand = (uint32_t)k_cand;
+    h.world = (uint32_t)world;
+    e = cudaMemcpy(buf, &h, sizeof(h), cudaMemcpyHostToDevice);
+  }
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e == cudaSuccess && ipc_handle) {
     cudaIpcMemHandle_t h;

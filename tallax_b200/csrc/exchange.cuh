@@ -23,8 +23,9 @@ constexpr int kExchangeMaxWorld = 16;
 struct ExchangeHeader {
   uint32_t step;     // steps completed on this rank; its low bit selects the set
   uint32_t done;     // merge CTAs that finished in the current step
-  uint32_t error;    // non-zero once a wait gave up
-  uint32_t pad[61];
+  uint32_t error;    // 1 once a wait gave up, 2 once a call's extents did not match the buffer's
+  uint32_t rows, k_cand, world;   // what the buffer was made for (tlx_exchange_create); the kernels check it
+  uint32_t pad[58];
 };
 static_assert(sizeof(ExchangeHeader) == 256, "header is one 256-byte block");
 

@@ -1831,6 +1831,15 @@ __global__ void __launch_bounds__(kMergeThreads) merge_and_sample_kernel(MergePa
     id = reinterpret_cast<const int32_t*>(v) + plane;
     un = v + 2 * plane;
     flag = reinterpret_cast<uint32_t*>(p.xbuf + p.off_flags[par]) + r;
+    // a call whose extents are not the buffer's reads nothing: token -1, status 2
+    if (xh->rows != (uint32_t)p.rows || xh->k_cand != (uint32_t)kpb || xh->world != (uint32_t)p.world) {
+      if (threadIdx.x == 0) {
+        atomicExch(&xh->error, 2u);
+        if (p.status) atomicExch(p.status, 2);
+        p.out[r] = -1;
+      }
+      return;
+    }
     if (threadIdx.x == 0) {
       // every rank's block of this row has arrived when the word reads `world`; two seconds at most
       const unsigned long long t0 = global_timer_ns();

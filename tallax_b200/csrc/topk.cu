@@ -52,7 +52,14 @@ __device__ __forceinline__ void emit_row(const TopkParams& p, int64_t r, const t
   const int K = p.k_max;
   const int k_row = p.k_per_row ? p.k_per_row[r] : K;
   uint32_t par = 0;   // which of the exchange buffer's two sets this step uses
-  if (p.ex.world > 0) par = reinterpret_cast<volatile const ExchangeHeader*>(p.ex.peer[p.ex.rank])->step & 1u;
+  bool deliver = p.ex.world > 0;
+  if (p.ex.world > 0) {
+    // a call whose extents are not the buffer's stores nothing anywhere and leaves a mark
+    volatile ExchangeHeader* h = reinterpret_cast<volatile ExchangeHeader*>(p.ex.peer[p.ex.rank]);
+    par = h->step & 1u;
+    deliver = h->rows == (uint32_t)p.rows && h->k_cand == (uint32_t)K && h->world == (uint32_t)p.ex.world;
+    if (!deliver && threadIdx.x == 0) h->error = 2u;
+  }
   for (int j = threadIdx.x; j < K; j += blockDim.x) {
     const uint64_t c = cand[j];
     const int32_t col = (int32_t)cand_low(c);
@@ -64,6 +71,7 @@ __device__ __forceinline__ void emit_row(const TopkParams& p, int64_t r, const t
       float u = 0.5f;
       if (have) u = p.noise.dense ? __ldg(p.noise.dense + r * p.noise.stride + col) : p.noise.at(r + p.dim0_offset, tok);
       if (p.ex.world > 0) {
+        if (!deliver) continue;
         // slot `rank` of every rank's buffer, this rank's own included, starting with the next rank
         const size_t plane = (size_t)p.rows * K;
         for (int i = 0; i < p.ex.world; ++i) {
@@ -89,7 +97,7 @@ __device__ __forceinline__ void emit_row(const TopkParams& p, int64_t r, const t
   if (p.ex.world > 0) {
     // the row's block is on its way to every rank: one arrival count each, released after the stores
     __syncthreads();
-    if ((int)threadIdx.x < p.ex.world) {
+    if (deliver && (int)threadIdx.x < p.ex.world) {
       __threadfence_system();
       atomicAdd_system(reinterpret_cast<uint32_t*>(p.ex.peer[threadIdx.x] + p.ex.off_flags[par]) + r, 1u);
     }

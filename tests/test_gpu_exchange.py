@@ -142,3 +142,25 @@ def test_exchange_steps_replayed_from_a_cuda_graph(cuda):
             assert ex.state() == (done, 0)
     finally:
         ex.close()
+
+
+def test_a_call_with_other_extents_than_the_buffers_touches_nothing(cuda):
+    import torch
+    from tallax_b200._src import ops
+    from tests.conftest import to_dev
+
+    dev = torch.device("cuda", 0)
+    B, V = 8, 4096
+    (ex,) = ops.Exchange.local_group(B, 16, 1, dev)
+    try:
+        x, tk, tp, T, noise = o.make_sharded_inputs(B=B, V=V, seed=5, dtype="bf16")
+        ex.k_cand = 32                      # the buffer was made for 16 candidates per row
+        ops.exchange_shard_candidates(to_dev(x, dev), 0, ex, noise_shard=to_dev(noise, dev), vocab_total=V)
+        tok = ops.exchange_merge_and_sample(ex, to_dev(np.minimum(tk, 16).astype(np.int32), dev), to_dev(tp, dev),
+                                            to_dev(T, dev))
+        torch.cuda.synchronize()
+        assert (tok.cpu().numpy() == -1).all()
+        assert int(ex.status.item()) == 2
+        assert ex.state() == (0, 2)          # no step was made, the mark is in the buffer
+    finally:
+        ex.close()
