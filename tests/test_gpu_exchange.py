@@ -164,3 +164,35 @@ def test_a_call_with_other_extents_than_the_buffers_touches_nothing(cuda):
         assert ex.state() == (0, 2)          # no step was made, the mark is in the buffer
     finally:
         ex.close()
+
+
+@pytest.mark.parametrize("world,k", [(2, 32), (4, 32), (8, 16), (3, 50)])
+def test_merge_of_sorted_blocks_with_ties_and_every_top_k(cuda, world, k):
+    """The merge places candidates without sorting: values in quarters (equal values across and inside the
+    shards' blocks, so the token order decides), top_k from 1 to all candidates and 0 (keep all), rows with a
+    temperature of 0.  Checked against the oracle's merge of the very same candidates."""
+    import torch
+    from tallax_b200._src import ops
+    from tests.conftest import to_dev, to_np
+
+    dev = torch.device("cuda", 0)
+    B, vl = 96, 1024
+    rng = np.random.default_rng(100 * world + k)
+    x = (np.round(rng.standard_normal((B, vl * world)).astype(np.float32) * 4) / 4).astype(o.bfloat16)
+    noise = rng.random((B, vl * world), dtype=np.float32)
+    gathered = torch.stack([ops.shard_candidates(to_dev(np.ascontiguousarray(x[:, r * vl:(r + 1) * vl]), dev), r * vl, k,
+                                                 noise_shard=to_dev(np.ascontiguousarray(noise[:, r * vl:(r + 1) * vl]), dev),
+                                                 vocab_total=vl * world) for r in range(world)])
+    tk = rng.integers(0, world * k + 1, B).astype(np.int32)      # 0 keeps all world * k candidates
+    tk[:4] = [1, world * k, k, 0]
+    tp = rng.uniform(0.5, 1.0, B).astype(np.float32)
+    T = rng.uniform(0.5, 1.5, B).astype(np.float32)
+    T[5] = 0.0
+    tok = to_np(ops.merge_and_sample(gathered, to_dev(tk, dev), to_dev(tp, dev), to_dev(T, dev)))
+    g = to_np(gathered)
+    cv = np.concatenate([g[s, 0] for s in range(world)], axis=1)
+    ci = np.concatenate([g[s, 1].view(np.int32) for s in range(world)], axis=1)
+    cn = np.concatenate([g[s, 2] for s in range(world)], axis=1)
+    exp, flags = o.merge_and_sample(cv, ci, cn, tk, tp, T, return_flags=True)
+    assert not ((tok != exp) & ~flags).any()
+    assert flags.mean() < 0.2
